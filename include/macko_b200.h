@@ -1,0 +1,120 @@
+/*
+ * macko_b200 -- C ABI of the sm_100a MACKO SpMV library (libmacko_b200.so).
+ *
+ * Every entry point
+ *   - is extern "C", takes plain pointers and sizes, returns an int status
+ *     (MACKO_OK == 0) and never throws or aborts;
+ *   - works on DEVICE pointers of the CUDA device that is current on the calling
+ *     thread, enqueues its work on `stream` (a cudaStream_t passed as void*,
+ *     NULL = legacy default stream) and returns without synchronising;
+ *   - allocates no device memory: the caller owns every buffer (inputs, outputs,
+ *     workspace), which keeps the calls legal inside CUDA-graph capture.
+ *
+ * MACKO compressed matrix (byte layout identical to the reference,
+ * src/macko_spmv/cuda/cpu_compressor.cuh:6-73 and
+ * src/macko_spmv/cuda/cpu_compressor_torch_launcher.cuh:34-38):
+ *   values       fp16  [P]      stored elements row after row, P % 8 == 0
+ *   deltas       uint8 [P/2]    4-bit zero-run before each stored element,
+ *                               element k in byte k/2, even k = low nibble
+ *   row_indices  int32 [rows+1] row r owns stored elements [ri[r], ri[r+1])
+ * Alignment required by the kernels: values 16 bytes, deltas 4 bytes,
+ * row_indices 4 bytes, x and y 2 bytes (16-byte aligned x is staged faster).
+ */
+#ifndef MACKO_B200_H_
+#define MACKO_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MACKO_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+
+enum macko_status {
+    MACKO_OK = 0,
+    MACKO_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, bad flag            */
+    MACKO_ERR_MISALIGNED = 2,       /* a buffer violates the alignment listed above     */
+    MACKO_ERR_SIZE_OVERFLOW = 3,    /* rows*cols or a count does not fit 31-bit indices */
+    MACKO_ERR_CUDA = 4,             /* a CUDA runtime call or the launch failed         */
+    MACKO_ERR_WORKSPACE = 5         /* workspace too small                              */
+};
+
+/* Library version (MACKO_B200_VERSION of the build). */
+int macko_version(void);
+
+/* Static text for a status code. */
+const char *macko_status_string(int status);
+
+/* Message describing the last non-OK status returned on the calling thread
+ * (thread-local, never NULL). */
+const char *macko_last_error(void);
+
+/*
+ * y = fp16( alpha * (M x) [+ beta * y] ),  fp32 accumulation.
+ *
+ * Replaces: kernel `macko_spmv<reuse_value_from_c>` (src/macko_spmv/cuda/kernels.cuh:34-124)
+ * and its host launcher `macko_spmv_launcher`
+ * (src/macko_spmv/cuda/kernels_torch_launchers.cuh:3-48, which fixes alpha=1, beta=0).
+ *
+ *   values, deltas, row_indices   compressed matrix on the device
+ *   padded_count                  P = number of fp16 in `values` (used for launch
+ *                                 heuristics and argument checks)
+ *   x  fp16[cols], y  fp16[rows]  device vectors; y is read only when beta != 0
+ * x must hold finite numbers for the result to be defined row by row (a non-finite
+ * x entry can turn any row into NaN, as in the reference kernel).
+ */
+int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_indices,
+                    int64_t rows, int64_t cols, int64_t padded_count,
+                    const void *x, void *y, float alpha, float beta, void *stream);
+
+/*
+ * Same product with the kernel shape chosen by the caller, for tuning sweeps:
+ *   lanes_per_row in {4, 8, 16, 32}; steps_in_flight in {1, 2, 4};
+ *   x_in_shared 0/1; ctas_per_sm >= 1 (0 = library default).
+ * No counterpart in the reference (its launch shape is fixed,
+ * kernels_torch_launchers.cuh:15-17).
+ */
+int macko_spmv_fp16_tuned(const void *values, const void *deltas, const int32_t *row_indices,
+                          int64_t rows, int64_t cols, int64_t padded_count,
+                          const void *x, void *y, float alpha, float beta, void *stream,
+                          int lanes_per_row, int steps_in_flight, int x_in_shared, int ctas_per_sm);
+
+/*
+ * GPU compressor, phase 1: per-row stored-element counts and their prefix sum.
+ *
+ * Replaces (together with macko_compress_emit): `compress_rows_cpu`
+ * (src/macko_spmv/cuda/cpu_compressor.cuh:6-73) and its tensor wrapper `cpu_compress`
+ * (src/macko_spmv/cuda/cpu_compressor_torch_launcher.cuh:6-39).
+ *
+ *   dense        fp16[rows*cols], row-major, contiguous, device memory
+ *   row_indices  int32[rows+1] out: ri[0]=0, ri[r+1]-ri[r] = stored elements of row r
+ * After the stream reaches this point, ri[rows] = n (unpadded stored count); the
+ * caller reads it back (one 4-byte copy) to size values/deltas: P = ceil(n/8)*8.
+ * rows*cols must be < 2^31 (the reference indexes with `int`).
+ */
+int macko_compress_count(const void *dense, int64_t rows, int64_t cols,
+                         int32_t *row_indices, void *stream);
+
+/* Bytes of scratch macko_compress_emit needs for a padded stored count P. */
+int64_t macko_compress_workspace_bytes(int64_t padded_count);
+
+/*
+ * GPU compressor, phase 2: write values[P] and deltas[P/2], bit-identical to the
+ * reference compressor on the same input (pads, nibble packing, NaN -> 0x7fff,
+ * zero tail up to the multiple of 8).
+ *   row_indices   output of macko_compress_count for the same `dense`
+ *   padded_count  P = ceil(ri[rows]/8)*8
+ *   workspace     device scratch of macko_compress_workspace_bytes(P) bytes,
+ *                 4-byte aligned; contents undefined afterwards
+ */
+int macko_compress_emit(const void *dense, int64_t rows, int64_t cols,
+                        const int32_t *row_indices, int64_t padded_count,
+                        void *values, void *deltas,
+                        void *workspace, int64_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MACKO_B200_H_ */

@@ -1,0 +1,128 @@
+"""B200-native MACKO SpMV: drop-in for the ``macko_spmv`` Python API.
+
+``compress(M)`` -> ``(values fp16[P], deltas uint8[P/2], row_indices int32[R+1], R, C)``
+``multiply(compressed, V)`` -> ``y`` fp16[R]
+``move_to_device(compressed, device)``
+
+Same functions, argument meaning and error behaviour as the reference
+(src/macko_spmv/__init__.py:110-149); same `macko_spmv::multiply` operator schema
+(src/macko_spmv/__init__.py:56-63). The kernels come from a prebuilt sm_100a library
+behind a C ABI (``include/macko_b200.h``) instead of an import-time JIT build; there is
+no CPU or PyTorch fallback: without the built libraries the import fails, and without a
+CUDA device every call raises.
+
+Use ``import macko_spmv_b200 as macko_spmv`` to switch an existing program over.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+LIB_NAME = "macko_spmv"
+__version__ = "0.1.0"
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_CORE_PATH = os.path.join(_PKG_DIR, "libmacko_b200.so")
+_OPS_PATH = os.path.join(_PKG_DIR, "_torch_ops.so")
+
+# The reference reads this variable to choose its JIT cache directory
+# (src/macko_spmv/__init__.py:12). Nothing is compiled at import here; it is accepted and ignored.
+BUILD_DIRECTORY = os.environ.get("MACKO_SPMV_BUILD_DIRECTORY", "")
+
+
+def _load_native():
+    for path in (_CORE_PATH, _OPS_PATH):
+        if not os.path.exists(path):
+            raise ImportError(
+                f"{path} is missing: build the native libraries first with "
+                "`python -m macko_spmv_b200.build` (needs nvcc and g++)."
+            )
+    core = ctypes.CDLL(_CORE_PATH, mode=ctypes.RTLD_GLOBAL)
+    torch.ops.load_library(_OPS_PATH)
+    return core
+
+
+_core = _load_native()
+_core.macko_version.restype = ctypes.c_int
+_core.macko_last_error.restype = ctypes.c_char_p
+_core.macko_status_string.restype = ctypes.c_char_p
+_core.macko_status_string.argtypes = [ctypes.c_int]
+
+
+def native_library_paths() -> tuple[str, str]:
+    """Paths of the C-ABI library and of the torch operator library that were loaded."""
+    return _CORE_PATH, _OPS_PATH
+
+
+def native_version() -> int:
+    return int(_core.macko_version())
+
+
+@torch.library.register_fake("macko_spmv::multiply")
+def _multiply_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, V):
+    # Same meta kernel as the reference (src/macko_spmv/__init__.py:105-107).
+    return torch.empty((M_rows,), device=M_values.device, dtype=M_values.dtype)
+
+
+@torch.library.register_fake("macko_spmv::compress_dense")
+def _compress_fake(M):
+    n = torch.library.get_ctx().new_dynamic_size()
+    return (
+        M.new_empty((n * 8,)),
+        M.new_empty((n * 4,), dtype=torch.uint8),
+        M.new_empty((M.shape[0] + 1,), dtype=torch.int32),
+    )
+
+
+def move_to_device(compressed, device):
+    """Move the three buffers of a compressed matrix (src/macko_spmv/__init__.py:110-117)."""
+    return (
+        compressed[0].to(device=device),
+        compressed[1].to(device=device),
+        compressed[2].to(device=device),
+        compressed[3],
+        compressed[4],
+    )
+
+
+def compress(M):
+    """Compress a contiguous fp16 matrix into the MACKO 5-tuple, on the device of ``M``.
+
+    Mirrors src/macko_spmv/__init__.py:120-131, except that the encoder runs on the GPU:
+    a CUDA matrix never leaves the device, and a CPU matrix is copied to the current CUDA
+    device, compressed there and copied back (there is no host encoder in this package).
+    The buffers are bit-identical to the reference's.
+    """
+    assert M.is_contiguous()
+    if M.device.type == "cuda":
+        values, deltas, row_indices = torch.ops.macko_spmv.compress_dense.default(M)
+        return (values, deltas, row_indices, M.size(0), M.size(1))
+    elif M.device.type == "cpu":
+        if not torch.cuda.is_available():
+            raise RuntimeError("macko_spmv_b200.compress needs a CUDA device: the encoder is a GPU kernel")
+        values, deltas, row_indices = torch.ops.macko_spmv.compress_dense.default(M.to("cuda"))
+        return move_to_device((values, deltas, row_indices, M.size(0), M.size(1)), "cpu")
+    else:
+        raise NotImplementedError()
+
+
+def multiply(compressed_M, V):
+    """y = M @ V for a compressed matrix and an fp16 CUDA vector (src/macko_spmv/__init__.py:134-149)."""
+    assert compressed_M[0].is_cuda
+    assert compressed_M[1].is_cuda
+    assert compressed_M[2].is_cuda
+    assert V.is_cuda
+    assert V.is_contiguous()
+    return torch.ops.macko_spmv.multiply.default(
+        compressed_M[0],
+        compressed_M[1],
+        compressed_M[2],
+        compressed_M[3],
+        compressed_M[4],
+        V,
+    )
+
+
+__all__ = ["compress", "multiply", "move_to_device", "native_library_paths", "native_version", "LIB_NAME"]

@@ -1,0 +1,30 @@
+// Shared host-side helpers of libmacko_b200: status reporting and per-device caches.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "macko_b200.h"
+
+namespace macko {
+
+constexpr int kMaxDevices = 64;
+
+// Thread-local text of the last failure (returned by macko_last_error()).
+char *last_error_buffer();
+int fail(int status, const char *fmt, ...);
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int max_smem_optin = 0;  // bytes of dynamic shared memory a CTA may opt in to
+    bool valid = false;
+};
+
+// Attributes of the current device, queried once per device.
+int current_device_info(const DeviceInfo **out);
+
+inline bool aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+}  // namespace macko

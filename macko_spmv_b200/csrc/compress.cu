@@ -1,0 +1,294 @@
+// GPU compressor producing MACKO buffers bit-identical to the reference host encoder
+// `compress_rows_cpu` (src/macko_spmv/cuda/cpu_compressor.cuh:6-73).
+//
+// The reference walks every row with a running zero counter. The same output follows from a
+// closed form that parallelises: a true non-zero at column c whose previous non-zero of the
+// row (or -1) is at c0 has gap g = c - c0 - 1; it emits floor(g/16) pads, sitting on columns
+// c0+16, c0+32, ... (value = the +-0 found there, delta 15), then itself with delta g mod 16.
+// Zeros after the last non-zero of a row emit nothing. NaNs are stored as 0x7fff, -0.0 counts
+// as zero (cpu_compressor.cuh:26-27,36).
+//
+// Phase 1 (count):  one warp per row -> stored elements per row -> prefix sum = row_indices.
+// Phase 2 (emit):   one warp per row -> values and one delta per byte into scratch;
+//                   a final pass packs two deltas per byte and zeroes the tail up to P.
+// A warp reads 256 columns per step (one 128-bit load per lane, aligned on the matrix
+// allocation, not on the row, so odd column counts still use vector loads).
+#include "common.cuh"
+
+#include <cuda_fp16.h>
+
+namespace macko {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+constexpr int kThreads = kWarpsPerCta * 32;
+constexpr int kColsPerLane = 8;
+constexpr int kColsPerStep = 32 * kColsPerLane;
+
+__device__ __forceinline__ bool is_nonzero(unsigned short h) { return (h & 0x7fffu) != 0; }
+__device__ __forceinline__ unsigned short canonical(unsigned short h)
+{
+    return ((h & 0x7fffu) > 0x7c00u) ? (unsigned short)0x7fffu : h;
+}
+
+// Loads the 8 fp16 of this lane for the step starting at global element index g0 (multiple
+// of 8 relative to the allocation start). Elements outside [lo, hi) read as zero.
+__device__ __forceinline__ void load8(const unsigned short *dense, long long g0, long long lo, long long hi,
+                                      long long total, unsigned short (&h)[8])
+{
+    if (g0 >= 0 && g0 + 8 <= total) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(dense + g0));
+        const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            h[2 * j] = (unsigned short)(w[j] & 0xffffu);
+            h[2 * j + 1] = (unsigned short)(w[j] >> 16);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (g0 + i < lo || g0 + i >= hi) h[i] = 0;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const long long g = g0 + i;
+            h[i] = (g >= lo && g < hi) ? __ldg(dense + g) : (unsigned short)0;
+        }
+    }
+}
+
+// Column (row-relative) of the last non-zero strictly before this lane's 8 columns.
+__device__ __forceinline__ int prev_nonzero_before_lane(unsigned any, int lane, int my_last_col, int carry)
+{
+    const unsigned lower = any & ((1u << lane) - 1u);
+    const int src = lower ? 31 - __clz(lower) : lane;
+    const int got = __shfl_sync(0xffffffffu, my_last_col, src);
+    return lower ? got : carry;
+}
+
+template <bool EMIT>
+__global__ void __launch_bounds__(kThreads)
+compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int cols, bool vec_ok,
+                     int *__restrict__ row_counts_out,           // !EMIT: count of row r at [r+1]
+                     const int *__restrict__ row_indices,        // EMIT
+                     unsigned short *__restrict__ values,        // EMIT
+                     unsigned char *__restrict__ nibbles)        // EMIT: one delta per byte
+{
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const long long total = (long long)rows * cols;
+    const long long row_lo = (long long)row * cols;
+    const long long row_hi = row_lo + cols;
+    // First step starts at the 8-element boundary at or below the row start.
+    const long long first = vec_ok ? (row_lo & ~7LL) : row_lo;
+
+    int carry_prev = -1;   // column of the last non-zero seen so far in this row
+    int count = 0;         // !EMIT: stored elements seen by this lane
+    int out = EMIT ? row_indices[row] : 0;  // EMIT: next output slot of the warp
+
+    for (long long step0 = first; step0 < row_hi; step0 += kColsPerStep) {
+        const long long g0 = step0 + (long long)lane * kColsPerLane;
+        unsigned short h[8];
+        load8(dense, g0, row_lo, row_hi, vec_ok ? total : 0 /* forces the scalar path */, h);
+        const int c0 = (int)(g0 - row_lo);  // column of h[0]; may be negative on the first step
+        unsigned nz = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) nz |= is_nonzero(h[i]) ? (1u << i) : 0u;
+        const unsigned any = __ballot_sync(0xffffffffu, nz != 0);
+        if (any == 0) continue;  // warp-uniform
+        const int my_last = c0 + (31 - __clz(nz | 1u));
+        int prev = prev_nonzero_before_lane(any, lane, my_last, carry_prev);
+        carry_prev = __shfl_sync(0xffffffffu, my_last, 31 - __clz(any));
+
+        // stored elements emitted by this lane in this step
+        int mine = 0;
+        {
+            int p = prev;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (nz & (1u << i)) {
+                    const int c = c0 + i;
+                    mine += ((c - p - 1) >> 4) + 1;
+                    p = c;
+                }
+            }
+        }
+        if (!EMIT) {
+            count += mine;
+        } else {
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            int k = out + incl - mine;
+            out += __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (nz & (1u << i)) {
+                    const int c = c0 + i;
+                    for (int p = prev + 16; p < c; p += 16) {  // pads keep the sign of the zero they sit on
+                        values[k] = __ldg(dense + row_lo + p);
+                        nibbles[k] = 15;
+                        ++k;
+                    }
+                    values[k] = canonical(h[i]);
+                    nibbles[k] = (unsigned char)((c - prev - 1) & 15);
+                    ++k;
+                    prev = c;
+                }
+            }
+        }
+    }
+    if (!EMIT) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
+        if (lane == 0) row_counts_out[row + 1] = count;
+    }
+}
+
+// In-place inclusive prefix sum over counts[1..rows]; counts[0] = 0. One CTA.
+__global__ void __launch_bounds__(1024) scan_rows_kernel(int *__restrict__ ri, int rows)
+{
+    __shared__ int warp_sums[32];
+    __shared__ int carry_s;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) { ri[0] = 0; carry_s = 0; }
+    __syncthreads();
+    for (int base = 0; base < rows; base += 1024) {
+        const int i = base + tid;
+        const int v = i < rows ? ri[i + 1] : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int s = warp_sums[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, s, o);
+                if (lane >= o) s += t;
+            }
+            warp_sums[lane] = s;  // inclusive over warps
+        }
+        __syncthreads();
+        const int carry = carry_s;
+        const int before = warp ? warp_sums[warp - 1] : 0;
+        if (i < rows) ri[i + 1] = carry + before + incl;
+        __syncthreads();
+        if (tid == 0) carry_s = carry + warp_sums[31];
+        __syncthreads();
+    }
+}
+
+// Packs 8 one-per-byte deltas into 4 bytes, zeroing everything at or beyond n = ri[rows];
+// also zeroes values[n..P).
+__global__ void __launch_bounds__(256)
+pack_kernel(const uint2 *__restrict__ nibbles8, const int *__restrict__ ri, int rows, int groups,
+            unsigned *__restrict__ deltas32, unsigned short *__restrict__ values)
+{
+    const int g = blockIdx.x * 256 + threadIdx.x;
+    if (g >= groups) return;
+    const int n = ri[rows];
+    const int k0 = g * 8;
+    unsigned packed = 0;
+    if (k0 < n) {
+        const uint2 b = nibbles8[g];
+        const unsigned w[2] = {b.x, b.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const unsigned d = (w[i >> 2] >> (8 * (i & 3))) & 15u;
+            if (k0 + i < n) packed |= d << (4 * i);
+        }
+    }
+    deltas32[g] = packed;
+    if (k0 + 8 > n) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (k0 + i >= n) values[k0 + i] = 0;
+    }
+}
+
+int check_dense(const void *dense, int64_t rows, int64_t cols)
+{
+    if (rows < 0 || cols < 0) return fail(MACKO_ERR_INVALID_ARGUMENT, "negative size (rows=%lld cols=%lld)", (long long)rows, (long long)cols);
+    if (rows > 0 && cols > 0 && rows > ((1LL << 31) - 1) / cols)
+        return fail(MACKO_ERR_SIZE_OVERFLOW, "rows*cols = %lld*%lld does not fit 31 bits", (long long)rows, (long long)cols);
+    if (rows >= (1LL << 31) - 1) return fail(MACKO_ERR_SIZE_OVERFLOW, "too many rows");
+    if (rows * cols > 0 && !dense) return fail(MACKO_ERR_INVALID_ARGUMENT, "null dense matrix");
+    if (!aligned(dense, 2)) return fail(MACKO_ERR_MISALIGNED, "dense must be 2-byte aligned");
+    return MACKO_OK;
+}
+
+int launch_error(const char *what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return MACKO_OK;
+}
+
+}  // namespace
+}  // namespace macko
+
+extern "C" {
+
+int macko_compress_count(const void *dense, int64_t rows, int64_t cols, int32_t *row_indices, void *stream)
+{
+    using namespace macko;
+    int st = check_dense(dense, rows, cols);
+    if (st != MACKO_OK) return st;
+    if (!row_indices) return fail(MACKO_ERR_INVALID_ARGUMENT, "null row_indices");
+    if (!aligned(row_indices, 4)) return fail(MACKO_ERR_MISALIGNED, "row_indices must be 4-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (rows > 0) {
+        const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+        compress_rows_kernel<false><<<grid, kThreads, 0, s>>>(
+            static_cast<const unsigned short *>(dense), (int)rows, (int)cols, aligned(dense, 16),
+            row_indices, nullptr, nullptr, nullptr);
+        st = launch_error("compress count launch");
+        if (st != MACKO_OK) return st;
+    }
+    scan_rows_kernel<<<1, 1024, 0, s>>>(row_indices, (int)rows);
+    return launch_error("row scan launch");
+}
+
+int64_t macko_compress_workspace_bytes(int64_t padded_count) { return padded_count < 0 ? 0 : padded_count; }
+
+int macko_compress_emit(const void *dense, int64_t rows, int64_t cols, const int32_t *row_indices,
+                        int64_t padded_count, void *values, void *deltas,
+                        void *workspace, int64_t workspace_bytes, void *stream)
+{
+    using namespace macko;
+    int st = check_dense(dense, rows, cols);
+    if (st != MACKO_OK) return st;
+    if (!row_indices) return fail(MACKO_ERR_INVALID_ARGUMENT, "null row_indices");
+    if (padded_count < 0 || padded_count % 8 != 0 || padded_count >= (1LL << 31))
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "padded_count %lld must be a non-negative multiple of 8 below 2^31", (long long)padded_count);
+    if (padded_count == 0) return MACKO_OK;
+    if (!values || !deltas || !workspace) return fail(MACKO_ERR_INVALID_ARGUMENT, "null output or workspace");
+    if (!aligned(values, 2) || !aligned(deltas, 4) || !aligned(workspace, 8))
+        return fail(MACKO_ERR_MISALIGNED, "values needs 2-, deltas 4-, workspace 8-byte alignment");
+    if (workspace_bytes < macko_compress_workspace_bytes(padded_count))
+        return fail(MACKO_ERR_WORKSPACE, "workspace has %lld bytes, %lld needed", (long long)workspace_bytes,
+                    (long long)macko_compress_workspace_bytes(padded_count));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (rows > 0) {
+        const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+        compress_rows_kernel<true><<<grid, kThreads, 0, s>>>(
+            static_cast<const unsigned short *>(dense), (int)rows, (int)cols, aligned(dense, 16),
+            nullptr, row_indices, static_cast<unsigned short *>(values), static_cast<unsigned char *>(workspace));
+        st = launch_error("compress emit launch");
+        if (st != MACKO_OK) return st;
+    }
+    const int groups = (int)(padded_count / 8);
+    pack_kernel<<<(groups + 255) / 256, 256, 0, s>>>(
+        static_cast<const uint2 *>(workspace), row_indices, (int)rows, groups,
+        static_cast<unsigned *>(deltas), static_cast<unsigned short *>(values));
+    return launch_error("pack launch");
+}
+}

@@ -1,0 +1,180 @@
+"""ctypes front-end of the CPU oracle (``liboracle.so``) and of the compiled
+reference compressor (``_ref/libref_compress.so``).
+
+TEST INFRASTRUCTURE ONLY: imported by the test-suite, the smoke check and the
+benchmark's CPU-baseline leg. The shipped package never imports this module.
+
+All matrices and vectors cross this boundary as numpy arrays of fp16 *bit
+patterns* (``uint16``) so that -0.0 and NaN payloads are compared as bits.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+_REF_PATH = os.path.join(_HERE, "_ref", "libref_compress.so")
+
+_u16p = ctypes.POINTER(ctypes.c_uint16)
+_u8p = ctypes.POINTER(ctypes.c_uint8)
+_i32p = ctypes.POINTER(ctypes.c_int32)
+_f64p = ctypes.POINTER(ctypes.c_double)
+_i64 = ctypes.c_int64
+
+
+def build(force: bool = False) -> None:
+    """Compile the oracle (and the reference compressor when its sources exist)."""
+    if force or not os.path.exists(_LIB_PATH) or (
+        os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "macko_oracle.c"))
+    ):
+        subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
+    elif not os.path.exists(_REF_PATH):
+        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+
+
+_lib = None
+_ref = None
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        lib = ctypes.CDLL(_LIB_PATH)
+        lib.oracle_compress_bound.restype = _i64
+        lib.oracle_compress_bound.argtypes = [_i64, _i64]
+        lib.oracle_compress_fp16.restype = _i64
+        lib.oracle_compress_fp16.argtypes = [_u16p, _i64, _i64, _u16p, _u8p, _i32p, ctypes.POINTER(_i64)]
+        lib.oracle_decompress_fp16.restype = None
+        lib.oracle_decompress_fp16.argtypes = [_u16p, _u8p, _i32p, _i64, _i64, _u16p]
+        lib.oracle_spmv_fp16.restype = None
+        lib.oracle_spmv_fp16.argtypes = [_u16p, _u8p, _i32p, _i64, _i64, _u16p, _f64p, _u16p, _f64p]
+        lib.oracle_dense_matvec_fp16.restype = None
+        lib.oracle_dense_matvec_fp16.argtypes = [_u16p, _i64, _i64, _u16p, _f64p]
+        lib.oracle_num_threads.restype = ctypes.c_int
+        _lib = lib
+    return _lib
+
+
+def have_reference() -> bool:
+    """True when the compiled, unmodified reference compressor is available."""
+    return os.path.exists(_REF_PATH)
+
+
+def _load_ref():
+    global _ref
+    if _ref is None:
+        ref = ctypes.CDLL(_REF_PATH)
+        ref.ref_compress_fp16.restype = _i64
+        ref.ref_compress_fp16.argtypes = [
+            _u16p, ctypes.c_int, ctypes.c_int,
+            ctypes.POINTER(_u16p), ctypes.POINTER(_u8p), ctypes.POINTER(_i32p), ctypes.POINTER(_i64),
+        ]
+        ref.ref_free.restype = None
+        ref.ref_free.argtypes = [ctypes.c_void_p]
+        _ref = ref
+    return _ref
+
+
+def _as_u16(a) -> np.ndarray:
+    a = np.asarray(a)
+    if a.dtype == np.float16:
+        a = a.view(np.uint16)
+    if a.dtype != np.uint16:
+        raise TypeError(f"expected fp16 bit patterns (uint16/float16), got {a.dtype}")
+    return np.ascontiguousarray(a)
+
+
+def num_threads() -> int:
+    return int(_load().oracle_num_threads())
+
+
+def compress(dense):
+    """Oracle compress: (values u16[P], deltas u8[P/2], row_indices i32[R+1], R, C)."""
+    lib = _load()
+    dense = _as_u16(dense)
+    assert dense.ndim == 2
+    rows, cols = dense.shape
+    bound = int(lib.oracle_compress_bound(rows, cols))
+    values = np.empty(bound, dtype=np.uint16)
+    deltas = np.empty(bound // 2, dtype=np.uint8)
+    ri = np.empty(rows + 1, dtype=np.int32)
+    n = _i64(0)
+    padded = int(lib.oracle_compress_fp16(
+        dense.ctypes.data_as(_u16p), rows, cols,
+        values.ctypes.data_as(_u16p), deltas.ctypes.data_as(_u8p), ri.ctypes.data_as(_i32p),
+        ctypes.byref(n)))
+    return values[:padded].copy(), deltas[: padded // 2].copy(), ri, rows, cols
+
+
+def ref_compress(dense):
+    """The reference's own ``compress_rows_cpu`` (cpu_compressor.cuh:6-73), same 5-tuple."""
+    ref = _load_ref()
+    dense = _as_u16(dense)
+    assert dense.ndim == 2
+    rows, cols = dense.shape
+    v, d, r = _u16p(), _u8p(), _i32p()
+    n = _i64(0)
+    padded = int(ref.ref_compress_fp16(dense.ctypes.data_as(_u16p), rows, cols,
+                                       ctypes.byref(v), ctypes.byref(d), ctypes.byref(r), ctypes.byref(n)))
+    try:
+        if padded > 0:
+            values = np.ctypeslib.as_array(v, shape=(padded,)).copy()
+            deltas = np.ctypeslib.as_array(d, shape=(padded // 2,)).copy()
+        else:  # the reference realloc()s to size 0, which frees and yields NULL
+            values = np.empty(0, dtype=np.uint16)
+            deltas = np.empty(0, dtype=np.uint8)
+        ri = np.ctypeslib.as_array(r, shape=(rows + 1,)).copy()
+    finally:
+        ref.ref_free(v)
+        ref.ref_free(d)
+        ref.ref_free(r)
+    return values, deltas, ri, rows, cols
+
+
+def decompress(compressed) -> np.ndarray:
+    """Dense fp16 bit patterns [R, C] rebuilt from a compressed 5-tuple."""
+    lib = _load()
+    values, deltas, ri, rows, cols = compressed
+    values = _as_u16(values)
+    deltas = np.ascontiguousarray(deltas, dtype=np.uint8)
+    ri = np.ascontiguousarray(ri, dtype=np.int32)
+    dense = np.empty((rows, cols), dtype=np.uint16)
+    lib.oracle_decompress_fp16(values.ctypes.data_as(_u16p), deltas.ctypes.data_as(_u8p),
+                               ri.ctypes.data_as(_i32p), rows, cols, dense.ctypes.data_as(_u16p))
+    return dense
+
+
+def spmv(compressed, x):
+    """(y float64[R], y fp16 bits u16[R], row L1 mass float64[R]) from compressed buffers."""
+    lib = _load()
+    values, deltas, ri, rows, cols = compressed
+    values = _as_u16(values)
+    deltas = np.ascontiguousarray(deltas, dtype=np.uint8)
+    ri = np.ascontiguousarray(ri, dtype=np.int32)
+    x = _as_u16(x)
+    assert x.shape == (cols,)
+    y64 = np.empty(rows, dtype=np.float64)
+    yh = np.empty(rows, dtype=np.uint16)
+    l1 = np.empty(rows, dtype=np.float64)
+    lib.oracle_spmv_fp16(values.ctypes.data_as(_u16p), deltas.ctypes.data_as(_u8p),
+                         ri.ctypes.data_as(_i32p), rows, cols, x.ctypes.data_as(_u16p),
+                         y64.ctypes.data_as(_f64p), yh.ctypes.data_as(_u16p), l1.ctypes.data_as(_f64p))
+    return y64, yh, l1
+
+
+def dense_matvec(dense, x) -> np.ndarray:
+    """float64 y = M x for a dense fp16 matrix (bit patterns)."""
+    lib = _load()
+    dense = _as_u16(dense)
+    x = _as_u16(x)
+    rows, cols = dense.shape
+    y = np.empty(rows, dtype=np.float64)
+    lib.oracle_dense_matvec_fp16(dense.ctypes.data_as(_u16p), rows, cols, x.ctypes.data_as(_u16p),
+                                 y.ctypes.data_as(_f64p))
+    return y
