@@ -1,0 +1,59 @@
+"""ctypes declarations of every entry point of ``include/macko_b200.h``.
+
+This is the binding a non-torch host would write: plain integers for device pointers
+(e.g. ``tensor.data_ptr()``), a ``cudaStream_t`` as an integer, ``int`` status back.
+``check(status)`` turns a non-zero status into ``MackoError`` carrying the library's message.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libmacko_b200.so")
+
+OK = 0
+ERR_INVALID_ARGUMENT = 1
+ERR_MISALIGNED = 2
+ERR_SIZE_OVERFLOW = 3
+ERR_CUDA = 4
+ERR_WORKSPACE = 5
+
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_f = ctypes.c_float
+_int = ctypes.c_int
+
+SIGNATURES = {
+    "macko_version": (_int, []),
+    "macko_status_string": (ctypes.c_char_p, [_int]),
+    "macko_last_error": (ctypes.c_char_p, []),
+    "macko_spmv_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp]),
+    "macko_spmv_fp16_tuned": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp, _int, _int, _int, _int]),
+    "macko_compress_count": (_int, [_vp, _i64, _i64, _vp, _vp]),
+    "macko_compress_workspace_bytes": (_i64, [_i64]),
+    "macko_compress_emit": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
+}
+
+
+class MackoError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"macko status {status}: {message}")
+        self.status = status
+
+
+def load(path: str = LIB_PATH) -> ctypes.CDLL:
+    """Load the C-ABI library and attach the signatures above."""
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: run `python -m macko_spmv_b200.build`")
+    lib = ctypes.CDLL(path)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+def check(lib: ctypes.CDLL, status: int) -> None:
+    if status != OK:
+        raise MackoError(status, lib.macko_last_error().decode())

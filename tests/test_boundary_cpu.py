@@ -1,0 +1,98 @@
+"""CPU tests of the drop-in boundary: the C-ABI library loads and exports what the header
+declares, argument validation answers with status codes before touching a device, and the
+Python surface mirrors the reference's functions, schema and error behaviour."""
+import os
+import re
+
+import pytest
+import torch
+
+import macko_spmv_b200 as macko_spmv
+from macko_spmv_b200 import cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "macko_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(macko_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = cabi.load()
+    names = _declared_functions()
+    assert "macko_spmv_fp16" in names and "macko_compress_emit" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/macko_b200.h but not exported"
+        assert n in cabi.SIGNATURES, f"{n} has no ctypes signature in cabi.py"
+    assert lib.macko_version() == 100
+    assert lib.macko_status_string(0) == b"ok"
+
+
+def test_argument_validation_returns_status_codes():
+    lib = cabi.load()
+    a16 = 0x1000  # fake, well-aligned "device pointers": validation must reject before any use
+    # negative sizes
+    assert lib.macko_spmv_fp16(a16, a16, a16, -1, 8, 0, a16, a16, 1.0, 0.0, None) == cabi.ERR_INVALID_ARGUMENT
+    assert b"negative" in lib.macko_last_error()
+    # P not a multiple of 8
+    assert lib.macko_spmv_fp16(a16, a16, a16, 4, 8, 12, a16, a16, 1.0, 0.0, None) == cabi.ERR_INVALID_ARGUMENT
+    # misaligned values / deltas / x
+    assert lib.macko_spmv_fp16(a16 + 8, a16, a16, 4, 8, 8, a16, a16, 1.0, 0.0, None) == cabi.ERR_MISALIGNED
+    assert lib.macko_spmv_fp16(a16, a16 + 2, a16, 4, 8, 8, a16, a16, 1.0, 0.0, None) == cabi.ERR_MISALIGNED
+    assert lib.macko_spmv_fp16(a16, a16, a16, 4, 8, 8, a16 + 1, a16, 1.0, 0.0, None) == cabi.ERR_MISALIGNED
+    # null pointers
+    assert lib.macko_spmv_fp16(a16, a16, None, 4, 8, 8, a16, a16, 1.0, 0.0, None) == cabi.ERR_INVALID_ARGUMENT
+    # sizes beyond 31-bit indexing
+    assert lib.macko_spmv_fp16(a16, a16, a16, 4, 8, 1 << 31, a16, a16, 1.0, 0.0, None) == cabi.ERR_SIZE_OVERFLOW
+    assert lib.macko_compress_count(a16, 1 << 20, 1 << 20, a16, None) == cabi.ERR_SIZE_OVERFLOW
+    assert lib.macko_compress_count(a16, 4, 4, None, None) == cabi.ERR_INVALID_ARGUMENT
+    # emit: P shape, workspace size
+    assert lib.macko_compress_emit(a16, 4, 4, a16, 12, a16, a16, a16, 12, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_compress_emit(a16, 4, 4, a16, 16, a16, a16, a16, 8, None) == cabi.ERR_WORKSPACE
+    assert lib.macko_compress_workspace_bytes(4096) == 4096
+    # tuned entry point: bad shape parameters are rejected (after validation, before launch)
+    assert lib.macko_spmv_fp16_tuned(a16, a16, a16, 4, 8, 8, a16, a16, 1.0, 0.0, None, 8, 2, 1, -1) == cabi.ERR_INVALID_ARGUMENT
+    # an empty matrix is a no-op
+    assert lib.macko_spmv_fp16(None, None, None, 0, 8, 0, None, None, 1.0, 0.0, None) == cabi.OK
+    with pytest.raises(cabi.MackoError):
+        cabi.check(lib, lib.macko_spmv_fp16(a16, a16, a16, -1, 8, 0, a16, a16, 1.0, 0.0, None))
+
+
+def test_python_surface_matches_reference():
+    assert macko_spmv.LIB_NAME == "macko_spmv"
+    for name in ("compress", "multiply", "move_to_device"):
+        assert callable(getattr(macko_spmv, name))
+    schema = str(torch.ops.macko_spmv.multiply.default._schema)
+    assert schema == ("macko_spmv::multiply(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, "
+                      "int M_rows, int M_cols, Tensor V) -> Tensor")
+
+
+def test_python_error_behaviour_without_gpu():
+    M = torch.zeros(4, 8, dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        macko_spmv.compress(M.t())  # not contiguous
+    with pytest.raises(NotImplementedError):
+        macko_spmv.compress(torch.zeros(4, 8, dtype=torch.float16, device="meta"))
+    comp = (torch.zeros(8, dtype=torch.float16), torch.zeros(4, dtype=torch.uint8),
+            torch.zeros(5, dtype=torch.int32), 4, 8)
+    with pytest.raises(AssertionError):
+        macko_spmv.multiply(comp, torch.zeros(8, dtype=torch.float16))  # CPU operands
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="CUDA"):
+            macko_spmv.compress(M)  # no host encoder: fails loudly instead of falling back
+    moved = macko_spmv.move_to_device(comp, "cpu")
+    assert len(moved) == 5 and moved[3] == 4 and moved[4] == 8
+
+
+def test_fake_tensor_tracing():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        v = torch.empty(64, dtype=torch.float16, device="cuda")
+        d = torch.empty(32, dtype=torch.uint8, device="cuda")
+        ri = torch.empty(11, dtype=torch.int32, device="cuda")
+        x = torch.empty(40, dtype=torch.float16, device="cuda")
+        y = torch.ops.macko_spmv.multiply.default(v, d, ri, 10, 40, x)
+        assert y.shape == (10,) and y.dtype == torch.float16 and y.device.type == "cuda"
