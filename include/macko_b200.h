@@ -70,7 +70,7 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
 
 /*
  * Same product with the kernel shape chosen by the caller, for tuning sweeps:
- *   lanes_per_row in {4, 8, 16, 32}; steps_in_flight in {1, 2, 4};
+ *   lanes_per_row in {4, 8, 16, 32}; steps_in_flight in {2, 4};
  *   x_in_shared 0/1; ctas_per_sm >= 1 (0 = library default).
  * No counterpart in the reference (its launch shape is fixed,
  * kernels_torch_launchers.cuh:15-17).
@@ -106,7 +106,7 @@ int64_t macko_compress_workspace_bytes(int64_t padded_count);
  *   row_indices   output of macko_compress_count for the same `dense`
  *   padded_count  P = ceil(ri[rows]/8)*8
  *   workspace     device scratch of macko_compress_workspace_bytes(P) bytes,
- *                 4-byte aligned; contents undefined afterwards
+ *                 8-byte aligned; contents undefined afterwards
  */
 int macko_compress_emit(const void *dense, int64_t rows, int64_t cols,
                         const int32_t *row_indices, int64_t padded_count,

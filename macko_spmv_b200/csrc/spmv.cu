@@ -9,16 +9,20 @@
 //   * a warp is split into 32/L groups of L lanes; each group walks one row at a time and
 //     picks its next row from the warp's range as soon as it runs out of work, so rows of
 //     different length inside a warp do not wait for each other;
-//   * one step of a lane = 8 stored elements: one 128-bit load of values and one 32-bit load
-//     of 8 deltas, both straight into registers; D steps are issued before any is consumed;
-//   * the 8 column offsets of a lane are produced with byte-SIMD integer arithmetic
+//   * one unit of a lane = 8 stored elements: one 128-bit load of values and one 32-bit load
+//     of 8 deltas, both straight into registers; 2 or 4 units per lane are issued before any
+//     is consumed, and the phases of the computation run over all of them (loads, prefix sums,
+//     scans, gathers) so that independent work hides shuffle and shared-memory latency;
+//   * the 8 column offsets of a unit are produced with byte-SIMD integer arithmetic
 //     (two multiplies give the prefix sums of the even and odd nibbles), already scaled to
-//     byte offsets into x; only the lane totals cross lanes (log2(L) shuffles);
-//   * x lives in shared memory, framed by zero padding so that masked-out elements read
-//     0 without per-element range checks; products use the fp16 x fp16 + fp32 fused
-//     multiply-add of sm_100 (no conversion instructions);
-//   * row boundaries that fall inside a lane's 8-element group are handled by masking the
-//     group once per step, only in warps that actually contain such a lane.
+//     byte offsets into x; only lane totals cross lanes, two units per shuffle;
+//   * the kernel is bound by instruction issue on the half-rate integer pipe and by shared-memory
+//     wavefronts, not by HBM, so per element it spends three instructions and none on that pipe:
+//     a dot-product instruction forms the address, one 16-bit shared load gathers x from a
+//     zero-framed copy (masked-out elements read 0 without range checks), and the sm_100
+//     fp16 x fp16 + fp32 fused multiply-add needs no conversions;
+//   * row boundaries that fall inside a unit are handled by masking that unit, only in warps
+//     that actually contain such a unit.
 #include "common.cuh"
 
 #include <cuda_fp16.h>
@@ -28,14 +32,22 @@ namespace {
 
 constexpr int kThreads = 512;        // threads per CTA
 constexpr int kWarpsPerCta = kThreads / 32;
-constexpr int kGroup = 8;            // stored elements per lane per step (128-bit value load)
-constexpr int kXPadFront = 8;        // zero fp16 slots in front of x[0]   (16 bytes keeps x 16B-aligned)
-constexpr int kXPadBack = 160;       // zero fp16 slots after x[cols-1]    (> 8 + 8*15 + 8)
+constexpr int kGroup = 8;            // stored elements per lane per sub-step (one 128-bit value load)
+constexpr int kXPadFront = 32;       // zero fp16 slots in front of x[0] (64 bytes: keeps x 16B-aligned)
+constexpr int kXPadBack = 160;       // zero fp16 slots after x[cols-1]  (> 8 * 16 + 8)
 
-__device__ __forceinline__ float fma_h(float acc, unsigned short a, unsigned short b)
+// acc += fp16(low or high half of vword) * fp16(low half of xbits): the sm_100 mixed-precision FMA
+// (exact fp16 product accumulated in fp32, round to nearest); the halves are split inside the asm so
+// that no repacking instructions are needed around it.
+template <int HALF>
+__device__ __forceinline__ float fma_h(float acc, unsigned vword, unsigned xbits)
 {
-    // sm_100 mixed-precision FMA: exact fp16 product added in fp32, round to nearest.
-    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(a), "h"(b));
+    if (HALF)
+        asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, h, xl, %0;}"
+            : "+f"(acc) : "r"(vword), "r"(xbits));
+    else
+        asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, l, xl, %0;}"
+            : "+f"(acc) : "r"(vword), "r"(xbits));
     return acc;
 }
 
@@ -54,52 +66,73 @@ __device__ __forceinline__ unsigned ldg_stream_u32(const unsigned *p)
     return r;
 }
 
-__device__ __forceinline__ unsigned short lds_u16(unsigned addr)
+__device__ __forceinline__ unsigned lds_u16(unsigned addr)
 {
-    unsigned short r;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(r) : "r"(addr));
+    unsigned r;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(r) : "r"(addr));
     return r;
 }
 
-// Zero the fp16 halves of a 128-bit group whose element index is outside [lo, hi).
-__device__ __forceinline__ void mask_values(uint4 &v, int lo, int hi)
+// c + byte `J` of a: one integer dot-product instruction extracts the byte and adds the base, and it
+// does not run on the (half-rate) integer ALU pipe the rest of the index arithmetic competes for.
+template <int J>
+__device__ __forceinline__ int add_byte(unsigned a, int c)
 {
-    unsigned *w = reinterpret_cast<unsigned *>(&v);
+    return __dp4a(a, 1u << (8 * J), (unsigned)c);
+}
+
+// Zero the deltas and the fp16 values of one 8-element unit outside element range [lo, hi).
+__device__ __forceinline__ void mask_unit(uint4 &v, unsigned &w, int lo, int hi)
+{
+    lo = min(max(lo, 0), kGroup);
+    hi = min(max(hi, 0), kGroup);
+    unsigned m = lo >= kGroup ? 0u : (0xffffffffu << (4 * lo));
+    if (hi < kGroup) m &= ~(0xffffffffu << (4 * hi));
+    w &= m;
+    unsigned *vw = reinterpret_cast<unsigned *>(&v);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        unsigned m = 0;
-        if (2 * j >= lo && 2 * j < hi) m |= 0x0000ffffu;
-        if (2 * j + 1 >= lo && 2 * j + 1 < hi) m |= 0xffff0000u;
-        w[j] &= m;
+        const unsigned lo16 = ((m >> (8 * j)) & 1u) * 0xffffu;
+        const unsigned hi16 = ((m >> (8 * j + 4)) & 1u) * 0xffff0000u;
+        vw[j] &= (lo16 | hi16);
     }
 }
 
-template <int L, int D, bool XS>
+// L     lanes per row (a warp walks 32/L rows at once)
+// NPAIR pairs of sub-steps per iteration; a sub-step of a group is 8*L consecutive stored elements,
+//       and the two sub-steps of a pair share one cross-lane scan (two 16-bit fields per register)
+// XS    x staged in shared memory (else gathered from global memory with explicit clamping)
+template <int L, int NPAIR, bool XS>
 __global__ void __launch_bounds__(kThreads, 2)
 spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
             const int *__restrict__ ri, const __half *__restrict__ x, __half *__restrict__ y,
             int rows, int cols, float alpha, float beta)
 {
     extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int STEP = kGroup * L;   // elements per group per sub-step
+    constexpr int D = 2 * NPAIR;       // sub-steps per iteration
+    constexpr int K = 32 / L;          // rows a warp walks at once
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int lig = lane & (L - 1);          // lane in group
     const int group_lane0 = lane & ~(L - 1); // first lane of my group
     constexpr unsigned kLeaders = (L == 32) ? 0x1u : (L == 16) ? 0x00010001u : (L == 8) ? 0x01010101u : 0x11111111u;
 
-    // ---- this warp's contiguous row range --------------------------------------------------
+    // ---- this warp's contiguous row range, dealt in blocks of K rows so that the groups of a warp
+    //      run out of rows together ------------------------------------------------------------------
     const long long n_warps = (long long)gridDim.x * kWarpsPerCta;
     const long long warp_id = (long long)blockIdx.x * kWarpsPerCta + (tid >> 5);
-    int row_next = (int)((long long)rows * warp_id / n_warps);
-    const int row_hi = (int)((long long)rows * (warp_id + 1) / n_warps);
+    const long long n_blocks = ((long long)rows + K - 1) / K;
+    int row_next = (int)min((long long)rows, (n_blocks * warp_id / n_warps) * K);
+    const int row_hi = (int)min((long long)rows, (n_blocks * (warp_id + 1) / n_warps) * K);
 
-    // Window of 32 row offsets held one per lane; row r of the window is read by shuffle.
+    // Window of 32 row offsets held one per lane; entry r of the window is read by shuffle.
     int win_base = row_next;
     int ri_reg = 0;
     if (row_next < row_hi) ri_reg = __ldg(ri + min(win_base + lane, rows));
 
-    // ---- stage x into shared memory ------------------------------------------------------
-    unsigned xs_addr = 0;  // shared-window byte address of x[0]
+    // ---- stage x into shared memory, framed by zeros ------------------------------------------------
+    int x_base = 0;  // shared-window byte address of the front padding
     if (XS) {
         __half *xs = reinterpret_cast<__half *>(smem);
         const int n_total = kXPadFront + cols + kXPadBack;
@@ -114,24 +147,25 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         } else {
             for (int i = tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
         }
-        xs_addr = (unsigned)__cvta_generic_to_shared(xs + kXPadFront);
+        x_base = (int)__cvta_generic_to_shared(xs);
         __syncthreads();
     }
+    const int b2max = 2 * (kXPadFront + cols);
 
-    // ---- per-group state -------------------------------------------------------------------
+    // ---- per-group state ------------------------------------------------------------------------------
     int my_row = -1;   // row being walked by my group (-1: none)
     int begin = 0;     // first stored element of the row
     int end = 0;       // one past the last stored element
-    int pos = 0;       // first element of the group's next step (multiple of 8)
-    int sum2 = 0;      // 2 * (sum of deltas of the row consumed so far)
-    float acc = 0.f;
+    int pos = 0;       // first element of the group's next iteration (multiple of 8)
+    int sum2 = 0;      // 2 * (sum of the deltas of the row consumed so far)
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 
     for (;;) {
-        // ---- groups that ran out of work finish their row and take the next one -----------
+        // ---- groups that ran out of work finish their row and take the next one ---------------------
         const bool need = pos >= end;
         const unsigned needmask = __ballot_sync(0xffffffffu, need);
         if (needmask) {
-            float total = acc;
+            float total = (acc0 + acc1) + (acc2 + acc3);
 #pragma unroll
             for (int o = L / 2; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
             if (need) {
@@ -140,7 +174,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                     if (beta != 0.f) r += beta * __half2float(y[my_row]);
                     y[my_row] = __float2half_rn(r);
                 }
-                acc = 0.f;
+                acc0 = acc1 = acc2 = acc3 = 0.f;
             }
             const int avail = row_hi - row_next;
             if (avail <= 0) {
@@ -169,12 +203,13 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
             }
         }
 
-        // ---- issue the loads of D steps -----------------------------------------------------
+        // ---- issue the loads of the whole iteration ------------------------------------------------------
         uint4 v[D];
         unsigned w[D];
+        const int ord0 = pos + lig * kGroup;
 #pragma unroll
         for (int s = 0; s < D; ++s) {
-            const int ord = pos + (s * L + lig) * kGroup;
+            const int ord = ord0 + s * STEP;
             v[s] = make_uint4(0u, 0u, 0u, 0u);
             w[s] = 0u;
             if (ord < end) {
@@ -182,83 +217,101 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 w[s] = ldg_stream_u32(deltas + (ord >> 3));
             }
         }
+        const int lo0 = begin - ord0;   // > 0: leading elements of sub-step 0 belong to the previous row
+        const int rem0 = end - ord0;    // elements of the row from ord0 on
+        // byte offset (relative to the front padding) of "column -1 + index" before the lane's first element
+        int run = sum2 + 2 * (ord0 - begin) + 2 * kXPadFront;
 
-        // ---- consume them ---------------------------------------------------------------------
 #pragma unroll
-        for (int s = 0; s < D; ++s) {
-            const int ord = pos + (s * L + lig) * kGroup;
-            const int lo = begin - ord;  // elements [0, lo) of the group belong to the previous row
-            const int hi = end - ord;    // elements [hi, 8) belong to the next row
-            const bool partial = (hi > 0) && (lo > 0 || hi < kGroup);
-            if (__any_sync(0xffffffffu, partial)) {
-                if (partial) {
-                    const int lo_c = max(lo, 0), hi_c = min(hi, kGroup);
-                    unsigned m = 0xffffffffu << (4 * lo_c);
-                    if (hi_c < kGroup) m &= ~(0xffffffffu << (4 * hi_c));
-                    w[s] &= m;
-                    mask_values(v[s], lo_c, hi_c);
-                }
+        for (int p = 0; p < NPAIR; ++p) {
+            // a pair in which no lane of the warp has an element left ends the iteration
+            if (p > 0 && !__any_sync(0xffffffffu, rem0 > 2 * p * STEP)) break;
+            // Byte-SIMD prefix sums of the 8 deltas of a unit, scaled by 2 (byte offsets into fp16 x):
+            //   ce byte j = 2*(inclusive prefix of element 2j)   + 2*(2j)
+            //   co byte j = 2*(inclusive prefix of element 2j+1) + 2*(2j+1)
+            unsigned ce[2], co[2], t2[2];
+#pragma unroll
+            for (int hs = 0; hs < 2; ++hs) {
+                const int s = 2 * p + hs;
+                const int lo = (s == 0) ? lo0 : 0;
+                const int rem = rem0 - s * STEP;
+                // units that straddle the row's first or last element: only warps that have one pay
+                if (__any_sync(0xffffffffu, rem > 0 && (lo > 0 || rem < kGroup))) mask_unit(v[s], w[s], lo, rem);
+                const unsigned e2 = (w[s] << 1) & 0x1e1e1e1eu;
+                const unsigned o2 = (w[s] >> 3) & 0x1e1e1e1eu;
+                const unsigned pe = e2 * 0x01010101u;
+                const unsigned po = o2 * 0x01010101u;
+                ce[hs] = pe + (po << 8) + 0x0c080400u;
+                co[hs] = pe + po + 0x0e0a0602u;
+                t2[hs] = (pe + po) >> 24;
             }
-            // Byte-SIMD prefix sums of the 8 deltas, scaled by 2 (byte offsets into fp16 x):
-            // ce byte j = 2*(incl. prefix of element 2j)   + 2*(2j)
-            // co byte j = 2*(incl. prefix of element 2j+1) + 2*(2j+1)
-            const unsigned e2 = (w[s] << 1) & 0x1e1e1e1eu;
-            const unsigned o2 = (w[s] >> 3) & 0x1e1e1e1eu;
-            const unsigned pe = e2 * 0x01010101u;
-            const unsigned po = o2 * 0x01010101u;
-            const unsigned ce = pe + (po << 8) + 0x0c080400u;
-            const unsigned co = pe + po + 0x0e0a0602u;
-            const int tot2 = (int)((pe + po) >> 24);
-
-            int inc = tot2;
+            // one scan for both sub-steps: lane totals packed as two 16-bit fields (each < 2^13)
+            const unsigned t = t2[0] | (t2[1] << 16);
+            unsigned inc = t;
 #pragma unroll
             for (int o = 1; o < L; o <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, inc, o, L);
-                if (lig >= o) inc += t;
+                const unsigned u = __shfl_up_sync(0xffffffffu, inc, o, L);
+                if (lig >= o) inc += u;
             }
-            const int group_tot2 = __shfl_sync(0xffffffffu, inc, L - 1, L);
-            // byte offset (from x[0]) of "column -1 + element index" for element 0 of this lane
-            int base2 = sum2 + (inc - tot2) + 2 * (ord - begin);
-            base2 = min(max(base2, -2 * kXPadFront), 2 * cols);
-            sum2 += group_tot2;
-
-            const unsigned *vw = reinterpret_cast<const unsigned *>(&v[s]);
-            if (XS) {
-                const unsigned a0 = xs_addr + (unsigned)base2;
+            const unsigned g = __shfl_sync(0xffffffffu, inc, L - 1, L);
+            const unsigned ex = inc - t;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const unsigned oe = __byte_perm(ce, 0u, 0x4440u + j);
-                    const unsigned oo = __byte_perm(co, 0u, 0x4440u + j);
-                    const unsigned short xe = lds_u16(a0 + oe);
-                    const unsigned short xo = lds_u16(a0 + oo);
-                    acc = fma_h(acc, (unsigned short)(vw[j] & 0xffffu), xe);
-                    acc = fma_h(acc, (unsigned short)(vw[j] >> 16), xo);
+            for (int hs = 0; hs < 2; ++hs) {
+                const int s = 2 * p + hs;
+                int b2 = run + (int)(hs ? (ex >> 16) : (ex & 0xffffu));
+                run += (int)(hs ? (g >> 16) : (g & 0xffffu)) + 2 * STEP;
+                b2 = min(max(b2, 0), b2max);   // keeps malformed input inside the padded x
+                const unsigned *vw = reinterpret_cast<const unsigned *>(&v[s]);
+                unsigned xe[4], xo[4];
+                if (XS) {
+                    const int a0 = b2 + x_base;
+                    xe[0] = lds_u16((unsigned)add_byte<0>(ce[hs], a0));
+                    xo[0] = lds_u16((unsigned)add_byte<0>(co[hs], a0));
+                    xe[1] = lds_u16((unsigned)add_byte<1>(ce[hs], a0));
+                    xo[1] = lds_u16((unsigned)add_byte<1>(co[hs], a0));
+                    xe[2] = lds_u16((unsigned)add_byte<2>(ce[hs], a0));
+                    xo[2] = lds_u16((unsigned)add_byte<2>(co[hs], a0));
+                    xe[3] = lds_u16((unsigned)add_byte<3>(ce[hs], a0));
+                    xo[3] = lds_u16((unsigned)add_byte<3>(co[hs], a0));
+                } else {
+                    const unsigned short *xg = reinterpret_cast<const unsigned short *>(x);
+                    const int cmax = cols - 1;
+                    const int a0 = b2 - 2 * kXPadFront;
+                    auto gather = [&](int off2) -> unsigned {
+                        return (unsigned)__ldg(xg + min(max(off2 >> 1, 0), cmax));
+                    };
+                    xe[0] = gather(add_byte<0>(ce[hs], a0));
+                    xo[0] = gather(add_byte<0>(co[hs], a0));
+                    xe[1] = gather(add_byte<1>(ce[hs], a0));
+                    xo[1] = gather(add_byte<1>(co[hs], a0));
+                    xe[2] = gather(add_byte<2>(ce[hs], a0));
+                    xo[2] = gather(add_byte<2>(co[hs], a0));
+                    xe[3] = gather(add_byte<3>(ce[hs], a0));
+                    xo[3] = gather(add_byte<3>(co[hs], a0));
                 }
-            } else {
-                const unsigned short *xg = reinterpret_cast<const unsigned short *>(x);
-                const int cmax = cols - 1;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int ce_j = (base2 + (int)__byte_perm(ce, 0u, 0x4440u + j)) >> 1;
-                    const int co_j = (base2 + (int)__byte_perm(co, 0u, 0x4440u + j)) >> 1;
-                    const unsigned short xe = __ldg(xg + min(max(ce_j, 0), cmax));
-                    const unsigned short xo = __ldg(xg + min(max(co_j, 0), cmax));
-                    acc = fma_h(acc, (unsigned short)(vw[j] & 0xffffu), xe);
-                    acc = fma_h(acc, (unsigned short)(vw[j] >> 16), xo);
-                }
+                acc0 = fma_h<0>(acc0, vw[0], xe[0]);
+                acc1 = fma_h<1>(acc1, vw[0], xo[0]);
+                acc2 = fma_h<0>(acc2, vw[1], xe[1]);
+                acc3 = fma_h<1>(acc3, vw[1], xo[1]);
+                acc0 = fma_h<0>(acc0, vw[2], xe[2]);
+                acc1 = fma_h<1>(acc1, vw[2], xo[2]);
+                acc2 = fma_h<0>(acc2, vw[3], xe[3]);
+                acc3 = fma_h<1>(acc3, vw[3], xo[3]);
             }
         }
-        pos += D * L * kGroup;
+        // delta sum consumed up to the end of the iteration (meaningless once the row is over)
+        sum2 = run - 2 * (ord0 + D * STEP - begin) - 2 * kXPadFront;
+        pos += D * STEP;
     }
 }
 
-template <int L, int D, bool XS>
+template <int L, int NPAIR, bool XS>
 int launch(const void *values, const void *deltas, const int32_t *ri, int rows, int cols,
            const void *x, void *y, float alpha, float beta, cudaStream_t stream,
            const DeviceInfo &dev, int ctas_per_sm)
 {
     const size_t smem = XS ? (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) : 0;
-    auto kernel = spmv_kernel<L, D, XS>;
+    auto kernel = spmv_kernel<L, NPAIR, XS>;
     if (smem > 48 * 1024) {
         // Idempotent and cheap; set on every call so that every device is covered.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -285,10 +338,9 @@ int launch_d(int D, const void *values, const void *deltas, const int32_t *ri, i
              const DeviceInfo &dev, int ctas_per_sm)
 {
     switch (D) {
-        case 1: return launch<L, 1, XS>(values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 2: return launch<L, 2, XS>(values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 4: return launch<L, 4, XS>(values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        default: return fail(MACKO_ERR_INVALID_ARGUMENT, "steps_in_flight must be 1, 2 or 4 (got %d)", D);
+        case 2: return launch<L, 1, XS>(values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 4: return launch<L, 2, XS>(values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        default: return fail(MACKO_ERR_INVALID_ARGUMENT, "steps_in_flight must be 2 or 4 (got %d)", D);
     }
 }
 
@@ -379,7 +431,6 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
     while (L > 4 && (rows * (long long)(L / 2) / 32 >= resident_warps || avg_row <= (long long)L * kGroup / 2)) L >>= 1;
     int D = 4;
     if (avg_row <= (long long)L * kGroup * 2) D = 2;
-    if (avg_row <= (long long)L * kGroup) D = 1;
     const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
     const bool xs = smem <= (size_t)dev->max_smem_optin;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
