@@ -39,7 +39,7 @@ UNIT = "us"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum over the 36 spmv launches of one step, from the
 # ncu capture summarised in profiles/spmv_sweep_launches.md (None until captured).
-NCU_STEP_TRAFFIC_BYTES = None
+NCU_STEP_TRAFFIC_BYTES = 2729971968
 
 
 def measured_hbm_peak():
@@ -265,6 +265,7 @@ def run_own_arm(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
 
     import macko_spmv_b200 as macko_spmv
@@ -413,7 +414,40 @@ def run_own_arm(args):
             line["geomean_speedup_vs_cublas"] = round(float(torch.tensor(sp).log().mean().exp()), 3)
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing NCCL down: destroying a communicator that a live CUDA graph still
+        # references can block forever, and every result has been printed by now.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def run_single_case(args):
+    """A few SpMVs on one synthetic matrix: the small workload profiler captures are taken on."""
+    import macko_spmv_b200 as macko_spmv
+    from macko_spmv_b200 import workloads
+
+    rows, cols, density = args.single.split(",")
+    rows, cols, density = int(rows), int(cols), float(density)
+    torch.cuda.set_device(0)
+    M = workloads.magnitude_pruned_matrix(rows, cols, density, seed=2999, device="cuda")
+    x = workloads.dense_vector(cols, 3001, "cuda")
+    comp = macko_spmv.compress(M)
+    for _ in range(max(args.warmup, 1)):
+        macko_spmv.multiply(comp, x)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        y = macko_spmv.multiply(comp, x)
+    e1.record()
+    torch.cuda.synchronize()
+    ref = M.float() @ x.float()
+    err = float((y.float() - ref).norm() / ref.norm())
+    nbytes = workloads.algorithmic_bytes(comp[0].numel(), rows, cols)
+    print(json.dumps({"single": [rows, cols, density], "us_warm_l2": e0.elapsed_time(e1) * 1000 / args.steps,
+                      "algorithmic_bytes": nbytes, "rel_l2_vs_dense_fp32": err}), flush=True)
 
 
 def main():
@@ -424,8 +458,12 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-per-case", action="store_true", help="skip the per-matrix cuBLAS comparison")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--single", default=None, metavar="ROWS,COLS,DENSITY",
+                    help="run only a few SpMVs on one matrix (small case for profiler captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.single:
+        run_single_case(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_own_arm(args)
