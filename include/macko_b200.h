@@ -113,6 +113,32 @@ int macko_compress_emit(const void *dense, int64_t rows, int64_t cols,
                         void *values, void *deltas,
                         void *workspace, int64_t workspace_bytes, void *stream);
 
+/*
+ * macko_compress_emit without a workspace argument, for hosts that cannot hand the library any
+ * scratch memory: a plug-in running inside an application that has already given every byte of
+ * device memory to its own pool, or a code path on which a cudaMalloc (which may stall the whole
+ * device) is not acceptable. The one-delta-per-byte scratch of phase 2 lives in an array built into
+ * the library instead (16 MiB of device memory per GPU that loads the library, held until the
+ * process exits), so padded_count may not exceed macko_compress_static_capacity() = 16 777 216
+ * stored elements (a dense 4096x4096 matrix just fits); larger counts are refused with
+ * MACKO_ERR_WORKSPACE. Same inputs, outputs and bit-exact result as macko_compress_emit. The
+ * function calls no cudaMalloc/cudaFree and no allocating library routine.
+ *
+ * The first call on each device looks up the device address of the built-in array; make that
+ * first call outside any stream capture. All calls on a device share the array and it keeps what
+ * the previous call left in it (nothing in it needs clearing between calls), so two calls whose
+ * kernels can overlap on the GPU - different streams without an ordering between them - race:
+ * order them, or use macko_compress_emit with separate workspaces.
+ *
+ * This entry point has no counterpart in the reference.
+ */
+int macko_compress_emit_static(const void *dense, int64_t rows, int64_t cols,
+                               const int32_t *row_indices, int64_t padded_count,
+                               void *values, void *deltas, void *stream);
+
+/* Largest padded_count macko_compress_emit_static accepts. */
+int64_t macko_compress_static_capacity(void);
+
 #ifdef __cplusplus
 }
 #endif

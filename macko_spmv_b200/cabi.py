@@ -33,6 +33,8 @@ SIGNATURES = {
     "macko_compress_count": (_int, [_vp, _i64, _i64, _vp, _vp]),
     "macko_compress_workspace_bytes": (_i64, [_i64]),
     "macko_compress_emit": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "macko_compress_emit_static": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
+    "macko_compress_static_capacity": (_i64, []),
 }
 
 

@@ -17,6 +17,8 @@
 
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 namespace macko {
 namespace {
 
@@ -232,6 +234,36 @@ int launch_error(const char *what)
     return MACKO_OK;
 }
 
+
+// ---- scratch for macko_compress_emit_static ------------------------------------------------------
+// One delta per byte for up to kStaticScratchBytes stored elements. The array lives in the module's
+// global memory: every device that loads the library carries it until the process exits.
+constexpr long long kStaticScratchBytes = 16ll << 20;
+static __device__ __align__(256) unsigned char g_emit_scratch[kStaticScratchBytes];
+
+// Device address of g_emit_scratch on the current device. In host code the array's name only stands
+// in for the symbol; the address a kernel may use has to be asked for, once per device, while that
+// device is current.
+int static_scratch_address(unsigned char **out)
+{
+    static unsigned char *addr[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(MACKO_ERR_CUDA, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_emit_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(MACKO_ERR_CUDA, "cudaGetSymbolAddress(g_emit_scratch): %s", cudaGetErrorString(e));
+        addr[dev] = static_cast<unsigned char *>(p);
+    }
+    *out = addr[dev];
+    return MACKO_OK;
+}
+
 }  // namespace
 }  // namespace macko
 
@@ -290,5 +322,46 @@ int macko_compress_emit(const void *dense, int64_t rows, int64_t cols, const int
         static_cast<const uint2 *>(workspace), row_indices, (int)rows, groups,
         static_cast<unsigned *>(deltas), static_cast<unsigned short *>(values));
     return launch_error("pack launch");
+}
+
+int64_t macko_compress_static_capacity(void) { return macko::kStaticScratchBytes; }
+
+int macko_compress_emit_static(const void *dense, int64_t rows, int64_t cols, const int32_t *row_indices,
+                               int64_t padded_count, void *values, void *deltas, void *stream)
+{
+    using namespace macko;
+    int st = check_dense(dense, rows, cols);
+    if (st != MACKO_OK) return st;
+    if (!row_indices) return fail(MACKO_ERR_INVALID_ARGUMENT, "null row_indices");
+    if (padded_count < 0 || padded_count % 8 != 0)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "padded_count %lld must be a non-negative multiple of 8", (long long)padded_count);
+    if (padded_count > kStaticScratchBytes)
+        return fail(MACKO_ERR_WORKSPACE,
+                    "padded_count %lld exceeds the built-in scratch of %lld stored elements; "
+                    "use macko_compress_emit with a caller-provided workspace",
+                    (long long)padded_count, (long long)kStaticScratchBytes);
+    if (padded_count == 0) return MACKO_OK;
+    if (!values || !deltas) return fail(MACKO_ERR_INVALID_ARGUMENT, "null output");
+    if (!aligned(values, 2) || !aligned(deltas, 4))
+        return fail(MACKO_ERR_MISALIGNED, "values needs 2-, deltas 4-byte alignment");
+    unsigned char *scratch = nullptr;
+    st = static_scratch_address(&scratch);   // first call on a device: resolves the symbol
+    if (st != MACKO_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Nothing in the scratch has to start at zero: the emit kernel writes every slot below
+    // n = row_indices[rows] and the pack kernel reads no slot at or above n.
+    if (rows > 0) {
+        const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+        compress_rows_kernel<true><<<grid, kThreads, 0, s>>>(
+            static_cast<const unsigned short *>(dense), (int)rows, (int)cols, aligned(dense, 16),
+            nullptr, row_indices, static_cast<unsigned short *>(values), scratch);
+        st = launch_error("compress emit (static scratch) launch");
+        if (st != MACKO_OK) return st;
+    }
+    const int groups = (int)(padded_count / 8);
+    pack_kernel<<<(groups + 255) / 256, 256, 0, s>>>(
+        reinterpret_cast<const uint2 *>(scratch), row_indices, (int)rows, groups,
+        static_cast<unsigned *>(deltas), static_cast<unsigned short *>(values));
+    return launch_error("pack (static scratch) launch");
 }
 }
