@@ -265,7 +265,7 @@ def run_own_arm(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
+        os.environ.pop("NCCL_DEBUG", None)  # keep NCCL banners off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
 
     import macko_spmv_b200 as macko_spmv

@@ -108,7 +108,7 @@ template <int L, int NPAIR, bool XS>
 __global__ void __launch_bounds__(kThreads, 2)
 spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
             const int *__restrict__ ri, const __half *__restrict__ x, __half *__restrict__ y,
-            int rows, int cols, float alpha, float beta)
+            int rows, int cols, int stored, float alpha, float beta)
 {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int STEP = kGroup * L;   // elements per group per sub-step
@@ -198,8 +198,9 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 }
                 const int rank = __popc(leaders & ((1u << group_lane0) - 1u));
                 const int nr = row_next + rank;
-                const int b = __shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31);
-                const int e = __shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31);
+                // offsets are clamped into [0, stored] so that a corrupt row_indices cannot send loads outside values/deltas
+                const int b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
+                const int e = min(__shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31), stored);
                 if (need) {
                     if (rank < take) {
                         my_row = nr; begin = b; end = e; pos = b & ~(kGroup - 1); sum2 = 0;
@@ -325,7 +326,7 @@ bool use_pdl()
 }
 
 template <int L, int NPAIR, bool XS>
-int launch(const void *values, const void *deltas, const int32_t *ri, int rows, int cols,
+int launch(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
            const void *x, void *y, float alpha, float beta, cudaStream_t stream,
            const DeviceInfo &dev, int ctas_per_sm)
 {
@@ -355,34 +356,34 @@ int launch(const void *values, const void *deltas, const int32_t *ri, int rows, 
     cfg.numAttrs = use_pdl() ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel,
         static_cast<const uint4 *>(values), static_cast<const unsigned *>(deltas), ri,
-        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, alpha, beta);
+        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "spmv launch: %s", cudaGetErrorString(e));
     return MACKO_OK;
 }
 
 template <int L, bool XS>
-int launch_d(int D, const void *values, const void *deltas, const int32_t *ri, int rows, int cols,
+int launch_d(int D, const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
              const void *x, void *y, float alpha, float beta, cudaStream_t stream,
              const DeviceInfo &dev, int ctas_per_sm)
 {
     switch (D) {
-        case 2: return launch<L, 1, XS>(values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 4: return launch<L, 2, XS>(values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 2: return launch<L, 1, XS>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 4: return launch<L, 2, XS>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
         default: return fail(MACKO_ERR_INVALID_ARGUMENT, "steps_in_flight must be 2 or 4 (got %d)", D);
     }
 }
 
 template <bool XS>
-int launch_l(int L, int D, const void *values, const void *deltas, const int32_t *ri, int rows, int cols,
+int launch_l(int L, int D, const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
              const void *x, void *y, float alpha, float beta, cudaStream_t stream,
              const DeviceInfo &dev, int ctas_per_sm)
 {
     switch (L) {
-        case 4: return launch_d<4, XS>(D, values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 8: return launch_d<8, XS>(D, values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 16: return launch_d<16, XS>(D, values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 32: return launch_d<32, XS>(D, values, deltas, ri, rows, cols, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 4: return launch_d<4, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 8: return launch_d<8, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 16: return launch_d<16, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 32: return launch_d<32, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
         default: return fail(MACKO_ERR_INVALID_ARGUMENT, "lanes_per_row must be 4, 8, 16 or 32 (got %d)", L);
     }
 }
@@ -432,9 +433,9 @@ int macko_spmv_fp16_tuned(const void *values, const void *deltas, const int32_t 
         return fail(MACKO_ERR_INVALID_ARGUMENT, "x does not fit shared memory (cols=%lld)", (long long)cols);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (x_in_shared)
-        return launch_l<true>(lanes_per_row, steps_in_flight, values, deltas, row_indices, (int)rows, (int)cols,
+        return launch_l<true>(lanes_per_row, steps_in_flight, values, deltas, row_indices, (int)rows, (int)cols, padded_count,
                               x, y, alpha, beta, s, *dev, ctas_per_sm);
-    return launch_l<false>(lanes_per_row, steps_in_flight, values, deltas, row_indices, (int)rows, (int)cols,
+    return launch_l<false>(lanes_per_row, steps_in_flight, values, deltas, row_indices, (int)rows, (int)cols, padded_count,
                            x, y, alpha, beta, s, *dev, ctas_per_sm);
 }
 
@@ -463,7 +464,7 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
     const bool xs = smem <= (size_t)dev->max_smem_optin;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (xs)
-        return launch_l<true>(L, D, values, deltas, row_indices, (int)rows, (int)cols, x, y, alpha, beta, s, *dev, 0);
-    return launch_l<false>(L, D, values, deltas, row_indices, (int)rows, (int)cols, x, y, alpha, beta, s, *dev, 0);
+        return launch_l<true>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
+    return launch_l<false>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
 }
 }

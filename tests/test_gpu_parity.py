@@ -308,3 +308,21 @@ def test_skewed_rows():
     _assert_buffers_equal(comp, comp_np, "skewed")
     x = workloads.dense_vector(cols, 5, "cuda")
     _check_y(macko_spmv.multiply(comp, x), comp_np, _u16(x), "skewed")
+
+
+def test_corrupt_row_indices_stay_in_bounds():
+    # Offsets outside [0, P] are clamped inside the kernel: rows that use them give garbage, but no
+    # load leaves the buffers and rows with intact offsets keep their exact result.
+    rows, cols = 256, 1024
+    M = workloads.bernoulli_matrix(rows, cols, 0.3, seed=21).cuda()
+    comp = macko_spmv.compress(M)
+    x = workloads.dense_vector(cols, 22, "cuda")
+    good = macko_spmv.multiply(comp, x)
+    ri = comp[2].clone()
+    ri[100] = 2 ** 30
+    ri[101] = -7
+    bad = macko_spmv.multiply((comp[0], comp[1], ri, rows, cols), x)
+    torch.cuda.synchronize()
+    keep = torch.ones(rows, dtype=torch.bool, device="cuda")
+    keep[99:102] = False
+    assert torch.equal(bad[keep], good[keep])
