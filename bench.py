@@ -280,15 +280,26 @@ def run_own_arm(args):
     # ---- one step, captured as a CUDA graph: 36 x (SpMV [+ all-gather of y]) -----------------
     ys_local = [torch.empty(c["hi"] - c["lo"], dtype=torch.float16, device=device) for c in cases]
     ys_full = [torch.empty(c["rows"], dtype=torch.float16, device=device) for c in cases] if world > 1 else ys_local
+    from macko_spmv_b200 import sharded
+
+    shards = [sharded.RowShard(c["comp"], c["lo"], c["hi"], c["rows"],
+                               [sharded.row_block(c["rows"], r, world) for r in range(world)]) for c in cases]
+    peer = None
+    if world > 1 and args.exchange == "peer":
+        peer = sharded.PeerGather(max(c["rows"] for c in cases), device)
 
     def step_eager():
         stream = torch.cuda.current_stream().cuda_stream
+        if peer is not None:   # SpMV with the exchange fused into its epilogue, then the flag wait
+            for sh, c in zip(shards, cases):
+                peer.multiply(sh, c["x"])
+            return
         for c, yl, yf in zip(cases, ys_local, ys_full):
             comp = c["comp"]
             cabi.check(lib, lib.macko_spmv_fp16(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(),
                                                 c["hi"] - c["lo"], c["cols"], comp[0].numel(),
                                                 c["x"].data_ptr(), yl.data_ptr(), 1.0, 0.0, stream))
-            if world > 1:
+            if world > 1 and peer is None:
                 dist.all_gather_into_tensor(yf, yl)
 
     side = torch.cuda.Stream()
@@ -334,15 +345,15 @@ def run_own_arm(args):
     # ---- end to end through the public API with host buffers ------------------------------------
     xs_host = [c["x"].cpu().pin_memory() for c in cases]
     ys_host = [torch.empty(c["rows"], dtype=torch.float16).pin_memory() for c in cases]
-    from macko_spmv_b200 import sharded
-
-    shards = [sharded.RowShard(c["comp"], c["lo"], c["hi"], c["rows"],
-                               [sharded.row_block(c["rows"], r, world) for r in range(world)]) for c in cases]
-
     def step_e2e():
         for c, sh, xh, yh in zip(cases, shards, xs_host, ys_host):
             xd = xh.to(device, non_blocking=True)
-            y = macko_spmv.multiply(c["comp"], xd) if world == 1 else sharded.multiply_sharded(sh, xd)
+            if world == 1:
+                y = macko_spmv.multiply(c["comp"], xd)
+            elif peer is not None:
+                y = peer.multiply(sh, xd)
+            else:
+                y = sharded.multiply_sharded(sh, xd)
             yh.copy_(y, non_blocking=True)
 
     for _ in range(3):
@@ -382,7 +393,7 @@ def run_own_arm(args):
             "config": {
                 "workload": "llama2-7b linear-layer sweep: shapes 4096x4096, 11008x4096, 4096x11008, 32000x4096 x "
                             "densities 0.1..0.9, per-row magnitude pruning; one step = one SpMV per matrix (36)",
-                "parallelism": "single GPU" if world == 1 else f"rows of every matrix split over {world} GPUs, NCCL all-gather of y after each SpMV",
+                "parallelism": "single GPU" if world == 1 else (f"rows of every matrix split over {world} GPUs; " + ("every SpMV kernel stores its y slice into all ranks' y over NVLink and ends when all slices have arrived (no collective)" if peer is not None else "NCCL all-gather of y after each SpMV")),
                 "l2": "inputs larger than L2: a step streams %.2f GB of distinct compressed data per GPU, each matrix once" % (step_bytes / 1e9),
                 "launch": "one CUDA graph per step" if graph is not None else "eager launches",
             },
@@ -458,6 +469,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-per-case", action="store_true", help="skip the per-matrix cuBLAS comparison")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: how the y slices are exchanged (fused peer stores, or NCCL all-gather)")
     ap.add_argument("--single", default=None, metavar="ROWS,COLS,DENSITY",
                     help="run only a few SpMVs on one matrix (small case for profiler captures)")
     args = ap.parse_args()

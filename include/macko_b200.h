@@ -139,6 +139,35 @@ int macko_compress_emit_static(const void *dense, int64_t rows, int64_t cols,
 /* Largest padded_count macko_compress_emit_static accepts. */
 int64_t macko_compress_static_capacity(void);
 
+/*
+ * Row-sharded product with the exchange fused into the kernel (several GPUs, one process each).
+ * Rank `rank` of `world` (<= 8) holds the compressed block of rows [row_offset, row_offset + rows)
+ * and the whole x. Instead of writing a local slice and calling a collective, the kernel stores
+ * every y value it produces into the full-y buffer of EVERY rank (`peer_y[p]`, device pointers
+ * that are valid on this device: peer-mapped / symmetric memory), and when its grid has finished it
+ * advances this rank's call counter and releases it into slot `rank` of every rank's flag array.
+ * `peer_flags[p]` points to at least world + 3 zero-initialised uint32 of rank p:
+ *   [0, world) arrival counters, [world] calls issued, [world+1] internal ticket, [world+2] error.
+ * `peer_y` and `peer_flags` are HOST arrays of `world` pointers, read during the call.
+ *
+ * The CTA of the grid that finishes last then stays until the arrival counters of all ranks have
+ * reached this rank's call counter, so the completion of the kernel means that this rank's full y
+ * is complete: nothing else has to be enqueued. The wait is bounded: if a rank never arrives it gives
+ * up after a few seconds of polling and sets flags[world + 2] to 1 + that rank; it never hangs the
+ * device. macko_peer_wait(local_flags, world, stream) enqueues the same bounded wait as a kernel of
+ * its own, for hosts that want to re-check arrival at a later point of the stream.
+ *
+ * Every rank must issue the same sequence of scatter calls. Alternate between two full-y
+ * buffers from one call to the next: a rank may start the next product while another still reads
+ * the previous y. cols must fit shared memory (as for the default kernel shape).
+ * No counterpart in the reference (it is single-GPU).
+ */
+int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_t *row_indices,
+                            int64_t rows, int64_t cols, int64_t padded_count, const void *x,
+                            void *const *peer_y, int64_t row_offset, uint32_t *const *peer_flags,
+                            int rank, int world, void *stream);
+int macko_peer_wait(uint32_t *local_flags, int world, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,8 @@ SIGNATURES = {
     "macko_compress_emit": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
     "macko_compress_emit_static": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "macko_compress_static_capacity": (_i64, []),
+    "macko_spmv_fp16_scatter": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _int, _int, _vp]),
+    "macko_peer_wait": (_int, [_vp, _int, _vp]),
 }
 
 

@@ -100,15 +100,28 @@ __device__ __forceinline__ void mask_unit(uint4 &v, unsigned &w, int lo, int hi)
     }
 }
 
+// Where a row-sharded launch delivers its slice of y: the full-y buffer of every rank (peer-mapped
+// device pointers) and every rank's flag words. world == 0 for an ordinary launch.
+constexpr int kMaxPeers = 8;
+struct Peers {
+    __half *y[kMaxPeers];
+    unsigned *flags[kMaxPeers];   // per rank: [0, world) arrival counters, [world] calls issued, [world+1] CTA ticket, [world+2] error
+    long long row_offset;         // first row of this rank's block in the full y
+    int world;
+    int rank;
+};
+
 // L     lanes per row (a warp walks 32/L rows at once)
 // NPAIR pairs of sub-steps per iteration; a sub-step of a group is 8*L consecutive stored elements,
 //       and the two sub-steps of a pair share one cross-lane scan (two 16-bit fields per register)
 // XS    x staged in shared memory (else gathered from global memory with explicit clamping)
-template <int L, int NPAIR, bool XS>
+// PEER  the epilogue stores every y value into the full-y buffer of all ranks over NVLink and, once the
+//       whole grid is done, bumps this rank's arrival counter on every rank (no collective call follows)
+template <int L, int NPAIR, bool XS, bool PEER>
 __global__ void __launch_bounds__(kThreads, 2)
 spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
             const int *__restrict__ ri, const __half *__restrict__ x, __half *__restrict__ y,
-            int rows, int cols, int stored, float alpha, float beta)
+            int rows, int cols, int stored, float alpha, float beta, const Peers peers)
 {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int STEP = kGroup * L;   // elements per group per sub-step
@@ -133,6 +146,12 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     const long long n_blocks = ((long long)rows + K - 1) / K;
     int row_next = (int)min((long long)rows, (n_blocks * warp_id / n_warps) * K);
     const int row_hi = (int)min((long long)rows, (n_blocks * (warp_id + 1) / n_warps) * K);
+
+    // PEER: rows of the whole CTA (its warps own consecutive ranges) and the staging area for their y
+    const long long cta_w0 = (long long)blockIdx.x * kWarpsPerCta;
+    const int cta_row_lo = (int)min((long long)rows, (n_blocks * cta_w0 / n_warps) * K);
+    const int cta_row_hi = (int)min((long long)rows, (n_blocks * (cta_w0 + kWarpsPerCta) / n_warps) * K);
+    __half *ystage = reinterpret_cast<__half *>(smem + (((size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) + 15) & ~(size_t)15));
 
     // Window of 32 row offsets held one per lane; entry r of the window is read by shuffle.
     int win_base = row_next;
@@ -179,8 +198,12 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
             if (need) {
                 if (my_row >= 0 && lig == 0) {
                     float r = alpha * total;
-                    if (beta != 0.f) r += beta * __half2float(y[my_row]);
-                    y[my_row] = __float2half_rn(r);
+                    if (PEER) {
+                        ystage[my_row - cta_row_lo] = __float2half_rn(r);   // delivered in bulk at the end
+                    } else {
+                        if (beta != 0.f) r += beta * __half2float(y[my_row]);
+                        y[my_row] = __float2half_rn(r);
+                    }
                 }
                 acc0 = acc1 = acc2 = acc3 = 0.f;
             }
@@ -312,6 +335,66 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         sum2 = run - 2 * (ord0 + D * STEP - begin) - 2 * kXPadFront;
         pos += D * STEP;
     }
+
+    if (PEER) {
+        // The CTA's rows are contiguous: copy its staged slice of y to every rank with coalesced stores
+        // (single 2-byte stores per row would flood NVLink with tiny packets).
+        __syncthreads();
+        const int n_mine = cta_row_hi - cta_row_lo;
+        for (int p = 0; p < peers.world; ++p) {
+            __half *dst = peers.y[p] + peers.row_offset + cta_row_lo;
+            for (int i = tid; i < n_mine; i += kThreads) dst[i] = ystage[i];
+        }
+        // After the CTA barrier one thread publishes the CTA's peer stores system-wide (the fence is
+        // cumulative over what the barrier ordered before it); the last CTA of the grid then advances
+        // this rank's call counter and releases it into every rank's arrival slot for this rank.
+        __shared__ unsigned last_cta_seq;
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            unsigned *mine = peers.flags[peers.rank];
+            const unsigned ticket = atomicAdd(mine + peers.world + 1, 1u);
+            unsigned seq = 0u;
+            if (ticket == gridDim.x - 1) {
+                seq = mine[peers.world] + 1u;
+                mine[peers.world] = seq;
+                mine[peers.world + 1] = 0u;
+                for (int p = 0; p < peers.world; ++p)   // release at system scope: ordered after everything above
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + peers.rank), "r"(seq) : "memory");
+            }
+            last_cta_seq = seq;
+        }
+        __syncthreads();
+        // The CTA that finished last stays until the slices of all other ranks have arrived, so the end of
+        // this kernel means that this rank's full y is complete. Its own flags are already out, so no rank
+        // waits for a kernel that waits for it; the wait is bounded and records who was missing.
+        const unsigned seq = last_cta_seq;
+        if (seq != 0u && tid < peers.world) {
+            unsigned *mine = peers.flags[peers.rank];
+            unsigned seen = 0u;
+            bool arrived = false;
+            for (unsigned spin = 0; spin < (1u << 23); ++spin) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + tid) : "memory");
+                if ((int)(seen - seq) >= 0) { arrived = true; break; }
+            }
+            if (!arrived) mine[peers.world + 2] = 1u + (unsigned)tid;
+        }
+    }
+}
+
+// Waits (bounded) until every rank's arrival counter has reached this rank's own call counter, i.e.
+// until all slices of the current row-sharded product have landed in this rank's full y.
+__global__ void peer_wait_kernel(unsigned *flags, int world)
+{
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    const unsigned expected = flags[world];
+    unsigned seen = 0;
+    for (unsigned spin = 0; spin < (1u << 23); ++spin) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + p) : "memory");
+        if ((int)(seen - expected) >= 0) return;
+    }
+    flags[world + 2] = 1u + (unsigned)p;   // gave up: the host can read which rank never arrived
 }
 
 // Overlap of consecutive launches (programmatic dependent launch) can be switched off with
@@ -325,13 +408,15 @@ bool use_pdl()
     return on;
 }
 
-template <int L, int NPAIR, bool XS>
+template <int L, int NPAIR, bool XS, bool PEER = false>
 int launch(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
            const void *x, void *y, float alpha, float beta, cudaStream_t stream,
-           const DeviceInfo &dev, int ctas_per_sm)
+           const DeviceInfo &dev, int ctas_per_sm, const Peers &peers = Peers{})
 {
-    const size_t smem = XS ? (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) : 0;
-    auto kernel = spmv_kernel<L, NPAIR, XS>;
+    size_t smem = XS ? (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) : 0;
+    if (PEER)  // staging area for a CTA's slice of y (a CTA never owns more rows than rows / #SMs + rounding)
+        smem = ((smem + 15) & ~(size_t)15) + (size_t)(rows / dev.sm_count + kWarpsPerCta * 8 + 8) * sizeof(__half);
+    auto kernel = spmv_kernel<L, NPAIR, XS, PEER>;
     if (smem > 48 * 1024) {
         // Idempotent and cheap; set on every call so that every device is covered.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -353,10 +438,12 @@ int launch(const void *values, const void *deltas, const int32_t *ri, int rows, 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = use_pdl() ? 1 : 0;
+    // The scatter variant ends with a CTA that waits for other GPUs; letting the next kernel move in
+    // early only takes SM slots away from it (measured: slower), so it launches without the overlap.
+    cfg.numAttrs = (use_pdl() && !PEER) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel,
         static_cast<const uint4 *>(values), static_cast<const unsigned *>(deltas), ri,
-        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta);
+        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta, peers);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "spmv launch: %s", cudaGetErrorString(e));
     return MACKO_OK;
@@ -466,5 +553,58 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
     if (xs)
         return launch_l<true>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
     return launch_l<false>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
+}
+
+int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_t *row_indices,
+                            int64_t rows, int64_t cols, int64_t padded_count, const void *x,
+                            void *const *peer_y, int64_t row_offset, uint32_t *const *peer_flags,
+                            int rank, int world, void *stream)
+{
+    using namespace macko;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "rank %d / world %d outside 1..%d", rank, world, kMaxPeers);
+    if (!peer_y || !peer_flags || row_offset < 0)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "null peer tables or negative row offset");
+    Peers peers = {};
+    for (int p = 0; p < world; ++p) {
+        if (!peer_y[p] || !peer_flags[p]) return fail(MACKO_ERR_INVALID_ARGUMENT, "null pointer for rank %d", p);
+        if (!aligned(peer_y[p], 2) || !aligned(peer_flags[p], 4))
+            return fail(MACKO_ERR_MISALIGNED, "peer buffers need 2-byte (y) and 4-byte (flags) alignment");
+        peers.y[p] = static_cast<__half *>(peer_y[p]);
+        peers.flags[p] = peer_flags[p];
+    }
+    peers.row_offset = row_offset;
+    peers.world = world;
+    peers.rank = rank;
+    int st = check_args(values, deltas, row_indices, rows, cols, padded_count, x, peer_y[rank]);
+    if (st != MACKO_OK) return st;
+    const DeviceInfo *dev = nullptr;
+    st = current_device_info(&dev);
+    if (st != MACKO_OK) return st;
+    const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
+    if (smem > (size_t)dev->max_smem_optin)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "cols=%lld does not fit shared memory in the scatter variant", (long long)cols);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // rows == 0 still has to signal: launch the kernel with an empty range (one CTA)
+    const long long avg_row = rows > 0 ? padded_count / rows : 0;
+    const bool wide = rows < 16384;
+    const bool deep = avg_row > (long long)(wide ? 32 : 8) * kGroup * 2;
+    const int r = (int)rows, c = (int)cols;
+    if (wide)
+        return deep ? launch<32, 2, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers)
+                    : launch<32, 1, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers);
+    return deep ? launch<8, 2, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers)
+                : launch<8, 1, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers);
+}
+
+int macko_peer_wait(uint32_t *local_flags, int world, void *stream)
+{
+    using namespace macko;
+    if (!local_flags || world < 1 || world > kMaxPeers)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "null flags or world %d outside 1..%d", world, kMaxPeers);
+    peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(local_flags, world);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "peer wait launch: %s", cudaGetErrorString(e));
+    return MACKO_OK;
 }
 }

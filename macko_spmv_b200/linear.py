@@ -1,0 +1,114 @@
+"""`MackoLinear`: a linear layer whose weight is stored in MACKO form, and helpers for the
+compressed-checkpoint layout of the reference.
+
+The reference's LLM scripts replace every `nn.Linear` of the attention and MLP blocks by a layer that
+calls `multiply` once per input vector through `torch.vmap`
+(python_scripts/util_run_pruned_llm.py:102-133) and store a compressed model as a state dict in which
+each `<name>.weight` is replaced by `<name>.c_0 … <name>.c_4` = values, deltas, row_indices, rows, cols
+(python_scripts/util_compress_llm.py:16-44). This module keeps that key layout, so checkpoints written
+by either implementation load in the other, and routes batches itself: inputs of shape [..., in]
+are flattened and multiplied vector by vector on the current stream (decode is the batch-1 case).
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+COMPRESSED_KEYS = ("c_0", "c_1", "c_2", "c_3", "c_4")
+
+
+class MackoLinear(nn.Module):
+    """y = x @ W^T (+ bias) with W [out_features, in_features] held as a MACKO compressed matrix."""
+
+    def __init__(self, compressed, bias: torch.Tensor | None = None):
+        super().__init__()
+        values, deltas, row_indices, rows, cols = compressed
+        self.out_features = int(rows)
+        self.in_features = int(cols)
+        self.register_buffer("c_0", values)
+        self.register_buffer("c_1", deltas)
+        self.register_buffer("c_2", row_indices)
+        self.bias = nn.Parameter(bias, requires_grad=False) if bias is not None else None
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear) -> "MackoLinear":
+        """Compress the (already pruned) fp16 weight of an `nn.Linear`."""
+        from . import compress
+
+        w = linear.weight.detach()
+        if w.dtype != torch.float16:
+            raise TypeError("MackoLinear stores fp16 weights; convert the layer with .half() first")
+        bias = linear.bias.detach().clone() if linear.bias is not None else None
+        return cls(compress(w.contiguous()), bias)
+
+    @classmethod
+    def from_state_dict_entry(cls, state_dict, prefix: str, device=None) -> "MackoLinear":
+        """Build the layer from the `<prefix>.c_0 … c_4` entries of a compressed checkpoint."""
+        parts = [state_dict[f"{prefix}.{k}"] for k in COMPRESSED_KEYS]
+        tensors = [p.to(device) if device is not None else p for p in parts[:3]]
+        bias = state_dict.get(f"{prefix}.bias")
+        if bias is not None and device is not None:
+            bias = bias.to(device)
+        return cls((tensors[0], tensors[1], tensors[2], int(parts[3]), int(parts[4])), bias)
+
+    @property
+    def compressed(self):
+        return (self.c_0, self.c_1, self.c_2, self.out_features, self.in_features)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from . import multiply
+
+        if x.shape[-1] != self.in_features:
+            raise RuntimeError(f"expected last dimension {self.in_features}, got {tuple(x.shape)}")
+        lead = x.shape[:-1]
+        flat = x.reshape(-1, self.in_features)
+        comp = self.compressed
+        if flat.shape[0] == 1:
+            y = multiply(comp, flat[0].contiguous()).unsqueeze(0)
+        else:
+            y = torch.stack([multiply(comp, flat[i].contiguous()) for i in range(flat.shape[0])])
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*lead, self.out_features)
+
+    def extra_repr(self) -> str:
+        stored = self.c_0.numel()
+        dense = self.out_features * self.in_features
+        return (f"in_features={self.in_features}, out_features={self.out_features}, "
+                f"stored={stored} ({2.5 * stored / max(2 * dense, 1):.3f} of dense bytes)")
+
+
+def compress_state_dict(state_dict, select=lambda name: ("self_attn" in name or "mlp" in name) and name.endswith(".weight")):
+    """Replace every selected 2-D fp16 `<name>.weight` by `<name>.c_0 … c_4`.
+
+    The default selection is the reference's (attention and MLP projections,
+    python_scripts/util_compress_llm.py:25-27). Tensors are compressed on the GPU and returned on the
+    CPU, ready for `torch.save`; everything else is passed through unchanged.
+    """
+    from . import compress, move_to_device
+
+    out = {}
+    for name, tensor in state_dict.items():
+        if select(name) and tensor.dim() == 2 and tensor.dtype == torch.float16:
+            comp = move_to_device(compress(tensor.contiguous().to("cuda")), "cpu")
+            prefix = name[: -len(".weight")]
+            for key, part in zip(COMPRESSED_KEYS, comp):
+                out[f"{prefix}.{key}"] = part
+        else:
+            out[name] = tensor
+    return out
+
+
+def compressed_prefixes(state_dict) -> list[str]:
+    """Module paths that hold a compressed weight in `state_dict`."""
+    return sorted({k[: -len(".c_0")] for k in state_dict if k.endswith(".c_0")})
+
+
+def replace_linears(model: nn.Module, state_dict, device="cuda") -> nn.Module:
+    """Swap the modules named by the compressed entries of `state_dict` for `MackoLinear` layers
+    (what `fix()` does in python_scripts/util_run_pruned_llm.py:123-133)."""
+    for prefix in compressed_prefixes(state_dict):
+        parent_path, _, leaf = prefix.rpartition(".")
+        parent = model.get_submodule(parent_path) if parent_path else model
+        setattr(parent, leaf, MackoLinear.from_state_dict_entry(state_dict, prefix, device))
+    return model

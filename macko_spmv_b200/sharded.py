@@ -115,3 +115,64 @@ def multiply_sharded(shard: RowShard, x: torch.Tensor, out: torch.Tensor | None 
         from . import multiply as multiply_fn
     y_local = multiply_fn(shard.compressed, x)
     return gather_rows(y_local, shard, out)
+
+
+class PeerGather:
+    """Row-sharded SpMV whose kernel stores y straight into every rank's full y over NVLink.
+
+    Replaces `multiply_sharded`'s NCCL all-gather by the fused epilogue of
+    `macko_spmv_fp16_scatter`: no collective call and no extra kernel (the last CTA of the grid waits
+    for the other ranks' flags before the kernel ends).
+    The full-y buffers and the flag words live in torch symmetric memory (peer-mapped on every rank).
+    Two y slots are used alternately, so the result of a call stays valid until the call after next.
+    """
+
+    def __init__(self, max_rows: int, device, group=None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import cabi
+
+        self._ctypes = ctypes
+        self.lib = cabi.load()
+        self.check = cabi.check
+        group = group if group is not None else dist.group.WORLD
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("PeerGather supports at most 8 ranks (one NVLink domain)")
+        self.max_rows = int(max_rows)
+        self.buf = symm_mem.empty((2, self.max_rows), dtype=torch.float16, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        pad = self.handle.get_signal_pad(self.rank)
+        pad.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        ptr_array = ctypes.c_void_p * self.world
+        base = [int(p) for p in self.handle.buffer_ptrs]
+        self._y_tables = [ptr_array(*[b + slot * self.max_rows * 2 for b in base]) for slot in (0, 1)]
+        # the flag words sit 1 KiB into each rank's signal pad, clear of the slots torch's own barriers use
+        self._flag_table = ptr_array(*[int(p) + 1024 for p in self.handle.signal_pad_ptrs])
+        self._local_flags = int(self.handle.signal_pad_ptrs[self.rank]) + 1024
+        self._slot = 0
+
+    def multiply(self, shard: RowShard, x: torch.Tensor) -> torch.Tensor:
+        """Full y (a view of the current slot, length shard.total_rows) after all ranks delivered."""
+        if shard.total_rows > self.max_rows:
+            raise ValueError(f"matrix has {shard.total_rows} rows, the exchange buffers hold {self.max_rows}")
+        comp = shard.compressed
+        stream = torch.cuda.current_stream().cuda_stream
+        slot = self._slot
+        self._slot ^= 1
+        self.check(self.lib, self.lib.macko_spmv_fp16_scatter(
+            comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
+            x.data_ptr(), self._y_tables[slot], shard.row_lo, self._flag_table, self.rank, self.world, stream))
+        # the kernel itself returns only after the slices of all ranks have landed (its last CTA waits)
+        return self.buf[slot, : shard.total_rows]
+
+    def error_flag(self) -> int:
+        """0, or 1 + the rank whose slice never arrived in some earlier wait (reads device memory)."""
+        pad = self.handle.get_signal_pad(self.rank).view(torch.int32)
+        return int(pad[256 + self.world + 2].item())

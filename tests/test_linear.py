@@ -1,0 +1,72 @@
+"""MackoLinear and the compressed-checkpoint key layout (CPU part: key handling; GPU part: numerics)."""
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+import oracle
+from macko_spmv_b200 import linear, workloads
+
+
+def _oracle_comp(W):
+    v, d, ri, r, c = oracle.compress(W.numpy().view(np.uint16))
+    return (torch.from_numpy(v.view(np.float16).copy()), torch.from_numpy(d.copy()), torch.from_numpy(ri.copy()), r, c)
+
+
+def test_checkpoint_key_layout_and_module_swap_cpu():
+    W = workloads.bernoulli_matrix(6, 40, 0.3, seed=3)
+    comp = _oracle_comp(W)   # the test builds the buffers with the oracle: no GPU needed for key handling
+    sd = {"model.layers.0.mlp.up_proj.c_0": comp[0], "model.layers.0.mlp.up_proj.c_1": comp[1],
+          "model.layers.0.mlp.up_proj.c_2": comp[2], "model.layers.0.mlp.up_proj.c_3": comp[3],
+          "model.layers.0.mlp.up_proj.c_4": comp[4], "model.norm.weight": torch.ones(40)}
+    assert linear.compressed_prefixes(sd) == ["model.layers.0.mlp.up_proj"]
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mlp = nn.Module()
+            self.mlp.up_proj = nn.Linear(40, 6, bias=False)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.model = nn.Module()
+            self.model.layers = nn.ModuleList([Block()])
+
+    net = linear.replace_linears(Net(), sd, device="cpu")
+    layer = net.model.layers[0].mlp.up_proj
+    assert isinstance(layer, linear.MackoLinear)
+    assert layer.in_features == 40 and layer.out_features == 6
+    assert torch.equal(layer.c_0.view(torch.int16), comp[0].view(torch.int16))
+    assert set(k for k in layer.state_dict()) == {"c_0", "c_1", "c_2"}
+    with pytest.raises(RuntimeError):
+        layer(torch.zeros(3, 41, dtype=torch.float16))
+
+
+@pytest.mark.gpu
+def test_macko_linear_forward_and_checkpoint_roundtrip(tmp_path):
+    torch.manual_seed(0)
+    lin = nn.Linear(512, 300, bias=True).half().cuda()
+    with torch.no_grad():
+        lin.weight.mul_((torch.rand_like(lin.weight) < 0.4).half())
+    layer = linear.MackoLinear.from_linear(lin)
+    x = torch.randn(2, 3, 512, device="cuda").half()
+    ref = torch.nn.functional.linear(x.float(), lin.weight.float(), lin.bias.float())
+    got = layer(x)
+    assert got.shape == (2, 3, 300)
+    assert torch.allclose(got.float(), ref, rtol=2e-3, atol=2e-3)
+    assert torch.allclose(layer(x[0, 0]).float(), ref[0, 0], rtol=2e-3, atol=2e-3)
+    # checkpoint: compress a state dict with the reference's key selection, save, load, rebuild
+    sd = {"model.layers.0.self_attn.q_proj.weight": lin.weight.detach().cpu(),
+          "model.layers.0.self_attn.q_proj.bias": lin.bias.detach().cpu(),
+          "model.embed_tokens.weight": torch.randn(10, 512).half()}
+    csd = linear.compress_state_dict(sd)
+    assert "model.layers.0.self_attn.q_proj.weight" not in csd and "model.embed_tokens.weight" in csd
+    assert csd["model.layers.0.self_attn.q_proj.c_3"] == 300 and csd["model.layers.0.self_attn.q_proj.c_4"] == 512
+    path = tmp_path / "compressed.pt"
+    torch.save(csd, path)
+    back = torch.load(path)
+    rebuilt = linear.MackoLinear.from_state_dict_entry(back, "model.layers.0.self_attn.q_proj", device="cuda")
+    assert torch.equal(rebuilt(x), got)
+    exp = oracle.compress(lin.weight.detach().cpu().numpy().view(np.uint16))
+    assert np.array_equal(back["model.layers.0.self_attn.q_proj.c_1"].numpy(), exp[1])
