@@ -26,6 +26,8 @@ constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
 constexpr int kColsPerLane = 8;
 constexpr int kColsPerStep = 32 * kColsPerLane;
+constexpr int kUnroll = 4;        // steps whose loads are in flight together
+constexpr int kStageElems = 320;  // stored elements of one step that fit the per-warp staging area
 
 __device__ __forceinline__ bool is_nonzero(unsigned short h) { return (h & 0x7fffu) != 0; }
 __device__ __forceinline__ unsigned short canonical(unsigned short h)
@@ -88,58 +90,84 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
     int count = 0;         // !EMIT: stored elements seen by this lane
     int out = EMIT ? row_indices[row] : 0;  // EMIT: next output slot of the warp
 
-    for (long long step0 = first; step0 < row_hi; step0 += kColsPerStep) {
-        const long long g0 = step0 + (long long)lane * kColsPerLane;
-        unsigned short h[8];
-        load8(dense, g0, row_lo, row_hi, vec_ok ? total : 0 /* forces the scalar path */, h);
-        const int c0 = (int)(g0 - row_lo);  // column of h[0]; may be negative on the first step
-        unsigned nz = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) nz |= is_nonzero(h[i]) ? (1u << i) : 0u;
-        const unsigned any = __ballot_sync(0xffffffffu, nz != 0);
-        if (any == 0) continue;  // warp-uniform
-        const int my_last = c0 + (31 - __clz(nz | 1u));
-        int prev = prev_nonzero_before_lane(any, lane, my_last, carry_prev);
-        carry_prev = __shfl_sync(0xffffffffu, my_last, 31 - __clz(any));
+    // EMIT: the stored elements of one step are gathered in shared memory and written out with
+    // coalesced stores (every lane writing its own few elements would issue many tiny stores).
+    __shared__ unsigned short stage_v[EMIT ? kWarpsPerCta : 1][EMIT ? kStageElems : 1];
+    __shared__ unsigned char stage_n[EMIT ? kWarpsPerCta : 1][EMIT ? kStageElems : 1];
+    const int wslot = EMIT ? (int)(threadIdx.x >> 5) : 0;
 
-        // stored elements emitted by this lane in this step
-        int mine = 0;
-        {
-            int p = prev;
+    for (long long group0 = first; group0 < row_hi; group0 += (long long)kUnroll * kColsPerStep) {
+        // all loads of kUnroll steps are issued before the first one is consumed
+        unsigned short hs[kUnroll][8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (nz & (1u << i)) {
-                    const int c = c0 + i;
-                    mine += ((c - p - 1) >> 4) + 1;
-                    p = c;
-                }
-            }
-        }
-        if (!EMIT) {
-            count += mine;
-        } else {
-            int incl = mine;
+        for (int u = 0; u < kUnroll; ++u)
+            load8(dense, group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane, row_lo, row_hi,
+                  vec_ok ? total : 0 /* forces the scalar path */, hs[u]);
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            int k = out + incl - mine;
-            out += __shfl_sync(0xffffffffu, incl, 31);
+        for (int u = 0; u < kUnroll; ++u) {
+            const long long g0 = group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane;
+            const unsigned short (&h)[8] = hs[u];
+            const int c0 = (int)(g0 - row_lo);  // column of h[0]; may be negative on the first step
+            unsigned nz = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (nz & (1u << i)) {
-                    const int c = c0 + i;
-                    for (int p = prev + 16; p < c; p += 16) {  // pads keep the sign of the zero they sit on
-                        values[k] = __ldg(dense + row_lo + p);
-                        nibbles[k] = 15;
-                        ++k;
+            for (int i = 0; i < 8; ++i) nz |= is_nonzero(h[i]) ? (1u << i) : 0u;
+            const unsigned any = __ballot_sync(0xffffffffu, nz != 0);
+            if (any == 0) continue;  // warp-uniform
+            const int my_last = c0 + (31 - __clz(nz | 1u));
+            int prev = prev_nonzero_before_lane(any, lane, my_last, carry_prev);
+            carry_prev = __shfl_sync(0xffffffffu, my_last, 31 - __clz(any));
+
+            // stored elements emitted by this lane in this step
+            int mine = 0;
+            {
+                int p = prev;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (nz & (1u << i)) {
+                        const int c = c0 + i;
+                        mine += ((c - p - 1) >> 4) + 1;
+                        p = c;
                     }
-                    values[k] = canonical(h[i]);
-                    nibbles[k] = (unsigned char)((c - prev - 1) & 15);
-                    ++k;
-                    prev = c;
                 }
+            }
+            if (!EMIT) {
+                count += mine;
+            } else {
+                int incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                const int step_total = __shfl_sync(0xffffffffu, incl, 31);
+                const bool staged = step_total <= kStageElems;   // warp-uniform; long pad runs go direct
+                int k = staged ? incl - mine : out + incl - mine;
+                unsigned short *vdst = staged ? stage_v[wslot] : values;
+                unsigned char *ndst = staged ? stage_n[wslot] : nibbles;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (nz & (1u << i)) {
+                        const int c = c0 + i;
+                        for (int p = prev + 16; p < c; p += 16) {  // pads keep the sign of the zero they sit on
+                            vdst[k] = __ldg(dense + row_lo + p);
+                            ndst[k] = 15;
+                            ++k;
+                        }
+                        vdst[k] = canonical(h[i]);
+                        ndst[k] = (unsigned char)((c - prev - 1) & 15);
+                        ++k;
+                        prev = c;
+                    }
+                }
+                if (staged) {
+                    __syncwarp();
+                    for (int i = lane; i < step_total; i += 32) {
+                        values[out + i] = stage_v[wslot][i];
+                        nibbles[out + i] = stage_n[wslot][i];
+                    }
+                    __syncwarp();
+                }
+                out += step_total;
             }
         }
     }
