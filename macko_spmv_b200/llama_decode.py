@@ -1,0 +1,199 @@
+"""Batch-1 decode of a Llama-2-architecture transformer whose linear layers run through `multiply`.
+
+The reference measures end-to-end tokens/s by swapping the attention/MLP projections of a pruned
+Llama-2-7B for MACKO layers and decoding under CUDA graphs (python_scripts/util_run_pruned_llm.py).
+No checkpoint is available offline, so this module builds the same architecture (RMSNorm, rotary
+embeddings, multi-head attention with a static KV cache, SwiGLU MLP) with seeded random weights
+N(0, 0.02), prunes every linear layer per row by magnitude to the requested density, compresses it on
+the GPU, and decodes greedily with one captured CUDA graph per token. Prompt tokens go through the
+same single-token step. It is a caller of the hot path, used to report tokens/s; it is not a model zoo.
+
+    python -m macko_spmv_b200.llama_decode --density 0.5 --layers 32
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import time
+
+import torch
+from torch import nn
+
+from . import compress, workloads
+from .linear import MackoLinear
+
+LLAMA2_7B = dict(hidden=4096, heads=32, ffn=11008, vocab=32000, layers=32, eps=1e-5, rope_theta=10000.0)
+
+
+def _pruned_linear(out_features: int, in_features: int, density: float, seed: int, device) -> nn.Module:
+    """A MackoLinear (density < 1) or a dense nn.Linear (density >= 1, the cuBLAS baseline)."""
+    w = workloads.magnitude_pruned_matrix(out_features, in_features, min(density, 1.0), seed, device=device)
+    if density >= 1.0:
+        lin = nn.Linear(in_features, out_features, bias=False, device=device, dtype=torch.float16)
+        with torch.no_grad():
+            lin.weight.copy_(w)
+        return lin
+    return MackoLinear(compress(w))
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, device):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=torch.float16, device=device), requires_grad=False)
+        self.eps = eps
+        self.dim = dim
+
+    def forward(self, x):
+        return torch.nn.functional.rms_norm(x, (self.dim,), self.weight, self.eps)
+
+
+class Block(nn.Module):
+    """One transformer block. q/k/v and gate/up are stored as one matrix each (rows concatenated), so a
+    token costs four SpMVs per block; the glue around them is kept to a handful of kernels."""
+
+    def __init__(self, cfg, density, seed, device, max_len):
+        super().__init__()
+        h, f = cfg["hidden"], cfg["ffn"]
+        self.heads = cfg["heads"]
+        self.head_dim = h // self.heads
+        self.hidden, self.ffn = h, f
+        self.qkv_proj = _pruned_linear(3 * h, h, density, seed + 0, device)
+        self.o_proj = _pruned_linear(h, h, density, seed + 3, device)
+        self.gate_up_proj = _pruned_linear(2 * f, h, density, seed + 4, device)
+        self.down_proj = _pruned_linear(h, f, density, seed + 6, device)
+        self.input_norm = RMSNorm(h, cfg["eps"], device)
+        self.post_norm = RMSNorm(h, cfg["eps"], device)
+        self.register_buffer("k_cache", torch.zeros(1, self.heads, max_len, self.head_dim, dtype=torch.float16, device=device))
+        self.register_buffer("v_cache", torch.zeros(1, self.heads, max_len, self.head_dim, dtype=torch.float16, device=device))
+
+    def forward(self, x, pos, cos, sin, mask):
+        # x [hidden]; pos int64[1] on the device (graph-friendly); cos/sin [head_dim] fp16; mask [1,1,1,max_len]
+        qkv = self.qkv_proj(self.input_norm(x)).view(3, self.heads, self.head_dim)
+        qk = _rope(qkv[:2], cos, sin)                       # q and k rotated together
+        self.k_cache.index_copy_(2, pos, qk[1].view(1, self.heads, 1, self.head_dim))
+        self.v_cache.index_copy_(2, pos, qkv[2].view(1, self.heads, 1, self.head_dim))
+        attn = torch.nn.functional.scaled_dot_product_attention(
+            qk[0].view(1, self.heads, 1, self.head_dim), self.k_cache, self.v_cache, attn_mask=mask)
+        x = x + self.o_proj(attn.reshape(-1))
+        gu = self.gate_up_proj(self.post_norm(x))
+        return x + self.down_proj(torch.nn.functional.silu(gu[: self.ffn]) * gu[self.ffn :])
+
+
+def _rope(t, cos, sin):
+    # rotate-half convention: (t1, t2) -> (t1*cos - t2*sin, t2*cos + t1*sin), cos/sin repeated over both halves
+    half = t.shape[-1] // 2
+    rot = torch.cat((-t[..., half:], t[..., :half]), dim=-1)
+    return t * cos + rot * sin
+
+
+class LlamaDecoder(nn.Module):
+    def __init__(self, density: float, cfg=None, layers=None, device="cuda", max_len=384, seed=4000,
+                 prune_lm_head=True):
+        super().__init__()
+        cfg = dict(LLAMA2_7B if cfg is None else cfg)
+        if layers is not None:
+            cfg["layers"] = layers
+        self.cfg, self.max_len, self.device = cfg, max_len, device
+        h = cfg["hidden"]
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.embed = (0.02 * torch.randn(cfg["vocab"], h, generator=g, device=device)).to(torch.float16)
+        self.blocks = nn.ModuleList([Block(cfg, density, seed + 100 * (i + 1), device, max_len) for i in range(cfg["layers"])])
+        self.norm = RMSNorm(h, cfg["eps"], device)
+        self.lm_head = _pruned_linear(cfg["vocab"], h, density if prune_lm_head else 1.0, seed + 7, device)
+        half = (h // cfg["heads"]) // 2
+        inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(half, device=device, dtype=torch.float32) / half))
+        ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+        ang = torch.cat((ang, ang), dim=-1)
+        self.cos_table, self.sin_table = ang.cos().to(torch.float16), ang.sin().to(torch.float16)
+        self.neg_inf = torch.tensor(float("-inf"), dtype=torch.float16, device=device)
+        self.zero = torch.zeros((), dtype=torch.float16, device=device)
+        self.positions = torch.arange(max_len, device=device)
+
+    def step(self, token, pos):
+        """token int64[1], pos int64[1] (device tensors) -> next token int64[1] (greedy)."""
+        x = self.embed.index_select(0, token)[0]
+        cos = self.cos_table.index_select(0, pos)[0]
+        sin = self.sin_table.index_select(0, pos)[0]
+        mask = torch.where(self.positions <= pos, self.zero, self.neg_inf).view(1, 1, 1, -1)
+        for blk in self.blocks:
+            x = blk(x, pos, cos, sin, mask)
+        logits = self.lm_head(self.norm(x))
+        return torch.argmax(logits.float(), dim=-1, keepdim=True)
+
+
+@torch.no_grad()
+def generate(model: LlamaDecoder, prompt: torch.Tensor, new_tokens: int, use_graph: bool = True):
+    """Feeds the prompt token by token, then generates greedily. Returns (tokens, seconds for the
+    generated part, seconds for the prompt part)."""
+    dev = model.device
+    token = torch.zeros(1, dtype=torch.int64, device=dev)
+    pos = torch.zeros(1, dtype=torch.int64, device=dev)
+    out_token = torch.zeros(1, dtype=torch.int64, device=dev)
+    graph = None
+    if use_graph:
+        token.copy_(prompt[:1])
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                out_token.copy_(model.step(token, pos))
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out_token.copy_(model.step(token, pos))
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            out_token.copy_(model.step(token, pos))
+
+    tokens = []
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(prompt.numel()):
+        token.copy_(prompt[i : i + 1])
+        pos.fill_(i)
+        run_step()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    for i in range(new_tokens):
+        token.copy_(out_token)
+        pos.fill_(prompt.numel() + i)
+        run_step()
+        tokens.append(out_token.clone())
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    return torch.cat(tokens), t2 - t1, t1 - t0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--density", type=float, default=0.5, help="1.0 = dense nn.Linear (cuBLAS) baseline")
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--prompt", type=int, default=128)
+    ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--dense-lm-head", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    t0 = time.perf_counter()
+    model = LlamaDecoder(args.density, layers=args.layers, max_len=args.prompt + args.new_tokens,
+                         prune_lm_head=not args.dense_lm_head)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t0
+    g = torch.Generator(device="cuda").manual_seed(4001)
+    prompt = torch.randint(0, model.cfg["vocab"], (args.prompt,), generator=g, device="cuda")
+    _, gen_s, prompt_s = generate(model, prompt, args.new_tokens, use_graph=not args.no_graph)
+    print(json.dumps({
+        "model": "llama-2-7b architecture, random init", "layers": args.layers, "density": args.density,
+        "lm_head": "dense" if args.dense_lm_head or args.density >= 1 else "pruned",
+        "prompt_tokens": args.prompt, "new_tokens": args.new_tokens,
+        "tokens_per_s": args.new_tokens / gen_s, "prompt_tokens_per_s": args.prompt / prompt_s,
+        "build_seconds": build_s, "memory_GB": torch.cuda.max_memory_allocated() / 1e9,
+        "cuda_graph": not args.no_graph,
+    }), flush=True)
+
+
+if __name__ == "__main__":
+    main()
