@@ -188,7 +188,7 @@ def per_case_numbers(cases, lib, peak_gbs):
 
 # --------------------------------------------------------------------------- CPU reference path
 
-def cpu_reference_path(steps: int, warmup: int):
+def cpu_reference_path(steps: int, warmup: int, gpu_cases=None):
     """The reference's CPU path on a bounded sample of the sweep: the reference compressor
     (compiled, unmodified; else the oracle port) followed by a dense fp32 torch.mv of the
     decompressed matrix, on the 4096x4096 layer at the 9 densities. Returns microseconds
@@ -212,6 +212,9 @@ def cpu_reference_path(steps: int, warmup: int):
         x = workloads.dense_vector(cols, 77 + di, "cpu").float()
         sample.append((dec, x))
     scale = sum(r * c for r, c in workloads.LLAMA7B_SHAPES) / float(rows * cols)
+    ref_gpu = None
+    if gpu_cases is not None and oracle.have_reference_kernel():
+        ref_gpu = reference_gpu_kernel_times(gpu_cases)
 
     def one_step():
         for dec, x in sample:
@@ -229,7 +232,35 @@ def cpu_reference_path(steps: int, warmup: int):
                   f"decompressed matrix, scaled x{scale:.2f} by dense elements to the whole sweep",
         "compress_us": t_comp * 1e6 * scale, "compress_threads": 1,
         "spmv_plus_compress_us": (t_mv + t_comp) * 1e6 * scale,
+        "reference_gpu_kernel": ref_gpu,
     }
+
+
+def reference_gpu_kernel_times(gpu_cases):
+    """Baseline only: the reference's own CUDA kernel (compiled unmodified for sm_100a into oracle/_ref)
+    on compressed matrices that already sit on the device, timed like the per-case numbers (rotating
+    cold copies). `gpu_cases`: dicts with "comp" (device 5-tuple), "x", "rows", "cols", "density"."""
+    import oracle
+
+    stream = torch.cuda.current_stream().cuda_stream
+    out = []
+    for c in gpu_cases:
+        comp, x = c["comp"], c["x"]
+        rows, cols = comp[3], comp[4]
+        if rows % 32 != 0:
+            continue   # the reference kernel reads past row_indices for such shapes
+        nbytes = 2.5 * comp[0].numel()
+        n_copy = max(2, min(48, int(300e6 / max(nbytes, 1)) + 1))
+        copies = [comp[:3]] + [tuple(t.clone() for t in comp[:3]) for _ in range(n_copy - 1)]
+        ys = [torch.empty(rows, dtype=torch.float16, device=x.device) for _ in range(n_copy)]
+        fns = [(lambda k=k, y=y: oracle.ref_spmv_gpu(k[0].data_ptr(), k[1].data_ptr(), k[2].data_ptr(), x.data_ptr(),
+                                                    y.data_ptr(), rows, cols, stream)) for k, y in zip(copies, ys)]
+        reps = max(30, min(200, int(1.5e9 / max(nbytes, 1))))
+        out.append({"shape": [rows, cols], "density": c["density"], "us": round(time_rotating(fns, reps), 2)})
+        del copies, ys
+    torch.cuda.empty_cache()
+    return {"kernel": "macko_spmv<false> of the reference, nvcc -arch sm_100a, reference launch shape",
+            "sum_us": round(sum(o["us"] for o in out), 1), "cases": out}
 
 
 def run_reference_arm(args):
@@ -382,7 +413,7 @@ def run_own_arm(args):
         assert err < 5e-3, f"timed kernel produced a wrong result (rel L2 {err})"
 
     per_case = per_case_numbers(cases, lib, peak_gbs) if (world == 1 and not args.no_per_case) else None
-    cpu_base = cpu_reference_path(3, 1) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
+    cpu_base = cpu_reference_path(3, 1, gpu_cases=cases) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
 
     if rank == 0:
         achieved = step_bytes * world / (ms_per_step * 1e-3) / 1e9 if world == 1 else step_bytes / (ms_per_step * 1e-3) / 1e9

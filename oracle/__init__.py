@@ -18,6 +18,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libref_compress.so")
+_REF_KERNEL_PATH = os.path.join(_HERE, "_ref", "libref_kernel.so")
 
 _u16p = ctypes.POINTER(ctypes.c_uint16)
 _u8p = ctypes.POINTER(ctypes.c_uint8)
@@ -32,7 +33,7 @@ def build(force: bool = False) -> None:
         os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "macko_oracle.c"))
     ):
         subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
-    elif not os.path.exists(_REF_PATH):
+    elif not os.path.exists(_REF_PATH) or not os.path.exists(_REF_KERNEL_PATH):
         subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
 
 
@@ -79,6 +80,29 @@ def _load_ref():
         ref.ref_free.argtypes = [ctypes.c_void_p]
         _ref = ref
     return _ref
+
+
+_ref_kernel = None
+
+
+def have_reference_kernel() -> bool:
+    """True when the reference's own SpMV kernel, compiled unmodified for sm_100a, is available."""
+    return os.path.exists(_REF_KERNEL_PATH)
+
+
+def ref_spmv_gpu(values_ptr: int, deltas_ptr: int, row_indices_ptr: int, x_ptr: int, y_ptr: int,
+                 rows: int, cols: int, stream: int = 0) -> None:
+    """Launch the reference kernel (kernels.cuh:34-124, reference launch shape) on device pointers.
+    rows must be a positive multiple of 32 (the reference reads past row_indices otherwise)."""
+    global _ref_kernel
+    if _ref_kernel is None:
+        lib = ctypes.CDLL(_REF_KERNEL_PATH)
+        lib.ref_macko_spmv_fp16.restype = ctypes.c_int
+        lib.ref_macko_spmv_fp16.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        _ref_kernel = lib
+    st = _ref_kernel.ref_macko_spmv_fp16(values_ptr, deltas_ptr, row_indices_ptr, x_ptr, y_ptr, rows, cols, stream)
+    if st != 0:
+        raise RuntimeError(f"reference kernel launch refused or failed (status {st})")
 
 
 def _as_u16(a) -> np.ndarray:

@@ -326,3 +326,23 @@ def test_corrupt_row_indices_stay_in_bounds():
     keep = torch.ones(rows, dtype=torch.bool, device="cuda")
     keep[99:102] = False
     assert torch.equal(bad[keep], good[keep])
+
+
+@pytest.mark.skipif(not oracle.have_reference_kernel(), reason="compiled reference kernel not present")
+def test_multiply_against_reference_gpu_kernel():
+    # y of this library vs y of the reference's own kernel (compiled unmodified for sm_100a) on the same
+    # compressed buffers; both round fp32 sums to fp16, in different summation orders.
+    for (rows, cols, d) in [(4096, 4096, 0.5), (1024, 8192, 0.1), (32000, 4096, 0.9), (64, 100, 0.02)]:
+        M = workloads.bernoulli_matrix(rows, cols, d, seed=rows + cols).cuda()
+        comp = macko_spmv.compress(M)
+        x = workloads.dense_vector(cols, 7, "cuda")
+        ours = macko_spmv.multiply(comp, x)
+        theirs = torch.full((rows,), float("nan"), dtype=torch.float16, device="cuda")
+        oracle.ref_spmv_gpu(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), x.data_ptr(), theirs.data_ptr(),
+                            rows, cols, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        l1 = M.float().abs() @ x.float().abs()
+        assert bool(((ours.float() - theirs.float()).abs() <= 2 * MAX_ABS_FACTOR * l1 + 1e-6).all()), (rows, cols, d)
+        ref = M.float() @ x.float()
+        assert float((theirs.float() - ref).norm() / ref.norm()) <= REL_L2
+        assert float((ours.float() - ref).norm() / ref.norm()) <= REL_L2
