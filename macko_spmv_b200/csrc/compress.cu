@@ -29,35 +29,48 @@ constexpr int kColsPerStep = 32 * kColsPerLane;
 constexpr int kUnroll = 4;        // steps whose loads are in flight together
 constexpr int kStageElems = 320;  // stored elements of one step that fit the per-warp staging area
 
-__device__ __forceinline__ bool is_nonzero(unsigned short h) { return (h & 0x7fffu) != 0; }
 __device__ __forceinline__ unsigned short canonical(unsigned short h)
 {
     return ((h & 0x7fffu) > 0x7c00u) ? (unsigned short)0x7fffu : h;
 }
 
-// Loads the 8 fp16 of this lane for the step starting at global element index g0 (multiple
-// of 8 relative to the allocation start). Elements outside [lo, hi) read as zero.
-__device__ __forceinline__ void load8(const unsigned short *dense, long long g0, long long lo, long long hi,
-                                      long long total, unsigned short (&h)[8])
+// Loads the 8 fp16 of this lane for the step starting at global element index g0 (a multiple of 8
+// relative to the allocation start on the vector path) as four packed words; elements outside the
+// allocation read as zero. Which of the 8 belong to the row is decided by row_bits().
+__device__ __forceinline__ void load8(const unsigned short *dense, long long g0, long long total, bool vec_ok,
+                                      unsigned (&w)[4])
 {
-    if (g0 >= 0 && g0 + 8 <= total) {
+    if (vec_ok && g0 >= 0 && g0 + 8 <= total) {
         const uint4 v = __ldg(reinterpret_cast<const uint4 *>(dense + g0));
-        const unsigned w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            h[2 * j] = (unsigned short)(w[j] & 0xffffu);
-            h[2 * j + 1] = (unsigned short)(w[j] >> 16);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (g0 + i < lo || g0 + i >= hi) h[i] = 0;
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
     } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const long long g = g0 + i;
-            h[i] = (g >= lo && g < hi) ? __ldg(dense + g) : (unsigned short)0;
+        for (int j = 0; j < 4; ++j) {
+            const long long g = g0 + 2 * j;
+            const unsigned lo16 = (g >= 0 && g < total) ? (unsigned)__ldg(dense + g) : 0u;
+            const unsigned hi16 = (g + 1 >= 0 && g + 1 < total) ? (unsigned)__ldg(dense + g + 1) : 0u;
+            w[j] = lo16 | (hi16 << 16);
         }
     }
+}
+
+// Bit i set <=> element g0 + i lies inside the row [lo, hi).
+__device__ __forceinline__ unsigned row_bits(long long g0, long long lo, long long hi)
+{
+    const int a = (int)min(max(lo - g0, 0LL), 8LL), b = (int)min(max(hi - g0, 0LL), 8LL);
+    return ((1u << b) - 1u) & ~((1u << a) - 1u);
+}
+
+// Bit i set <=> fp16 element i of the four packed words is not +-0.
+__device__ __forceinline__ unsigned nonzero_bits(const unsigned (&w)[4])
+{
+    unsigned nz = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const unsigned t = __vsetne2(w[j] & 0x7fff7fffu, 0u);   // 1 per non-zero halfword
+        nz |= ((t & 1u) | (t >> 15)) << (2 * j);
+    }
+    return nz & 0xffu;
 }
 
 // Column (row-relative) of the last non-zero strictly before this lane's 8 columns.
@@ -98,38 +111,26 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
 
     for (long long group0 = first; group0 < row_hi; group0 += (long long)kUnroll * kColsPerStep) {
         // all loads of kUnroll steps are issued before the first one is consumed
-        unsigned short hs[kUnroll][8];
+        unsigned ws[kUnroll][4];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
-            load8(dense, group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane, row_lo, row_hi,
-                  vec_ok ? total : 0 /* forces the scalar path */, hs[u]);
+            load8(dense, group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane, total, vec_ok, ws[u]);
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const long long g0 = group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane;
-            const unsigned short (&h)[8] = hs[u];
-            const int c0 = (int)(g0 - row_lo);  // column of h[0]; may be negative on the first step
-            unsigned nz = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) nz |= is_nonzero(h[i]) ? (1u << i) : 0u;
+            const unsigned (&w)[4] = ws[u];
+            const int c0 = (int)(g0 - row_lo);  // column of element 0; may be negative on the first step
+            const unsigned nz = nonzero_bits(w) & row_bits(g0, row_lo, row_hi);
             const unsigned any = __ballot_sync(0xffffffffu, nz != 0);
             if (any == 0) continue;  // warp-uniform
             const int my_last = c0 + (31 - __clz(nz | 1u));
             int prev = prev_nonzero_before_lane(any, lane, my_last, carry_prev);
             carry_prev = __shfl_sync(0xffffffffu, my_last, 31 - __clz(any));
 
-            // stored elements emitted by this lane in this step
-            int mine = 0;
-            {
-                int p = prev;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (nz & (1u << i)) {
-                        const int c = c0 + i;
-                        mine += ((c - p - 1) >> 4) + 1;
-                        p = c;
-                    }
-                }
-            }
+            // stored elements emitted by this lane in this step: one per non-zero, plus the pads in
+            // front of its first non-zero (later ones follow within 8 columns, so they need none)
+            int mine = __popc(nz);
+            if (nz) mine += (c0 + (__ffs(nz) - 1) - prev - 1) >> 4;
             if (!EMIT) {
                 count += mine;
             } else {
@@ -153,7 +154,7 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
                             ndst[k] = 15;
                             ++k;
                         }
-                        vdst[k] = canonical(h[i]);
+                        vdst[k] = canonical((unsigned short)((w[i >> 1] >> (16 * (i & 1))) & 0xffffu));
                         ndst[k] = (unsigned char)((c - prev - 1) & 15);
                         ++k;
                         prev = c;
@@ -178,18 +179,27 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
     }
 }
 
-// In-place inclusive prefix sum over counts[1..rows]; counts[0] = 0. One CTA.
+// In-place inclusive prefix sum over counts[1..rows]; counts[0] = 0. One CTA, four rows per thread
+// and iteration.
 __global__ void __launch_bounds__(1024) scan_rows_kernel(int *__restrict__ ri, int rows)
 {
     __shared__ int warp_sums[32];
     __shared__ int carry_s;
+    constexpr int kPerThread = 4;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) { ri[0] = 0; carry_s = 0; }
     __syncthreads();
-    for (int base = 0; base < rows; base += 1024) {
-        const int i = base + tid;
-        const int v = i < rows ? ri[i + 1] : 0;
-        int incl = v;
+    for (int base = 0; base < rows; base += 1024 * kPerThread) {
+        const int i0 = base + tid * kPerThread;
+        int v[kPerThread];
+        int mine = 0;
+#pragma unroll
+        for (int k = 0; k < kPerThread; ++k) {
+            v[k] = i0 + k < rows ? ri[i0 + k + 1] : 0;
+            mine += v[k];
+            v[k] = mine;            // inclusive within the thread
+        }
+        int incl = mine;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const int t = __shfl_up_sync(0xffffffffu, incl, o);
@@ -207,11 +217,12 @@ __global__ void __launch_bounds__(1024) scan_rows_kernel(int *__restrict__ ri, i
             warp_sums[lane] = s;  // inclusive over warps
         }
         __syncthreads();
-        const int carry = carry_s;
-        const int before = warp ? warp_sums[warp - 1] : 0;
-        if (i < rows) ri[i + 1] = carry + before + incl;
+        const int before = carry_s + (warp ? warp_sums[warp - 1] : 0) + incl - mine;
+#pragma unroll
+        for (int k = 0; k < kPerThread; ++k)
+            if (i0 + k < rows) ri[i0 + k + 1] = before + v[k];
         __syncthreads();
-        if (tid == 0) carry_s = carry + warp_sums[31];
+        if (tid == 0) carry_s += warp_sums[31];
         __syncthreads();
     }
 }
