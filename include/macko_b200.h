@@ -70,7 +70,7 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
 
 /*
  * Same product with the kernel shape chosen by the caller, for tuning sweeps:
- *   lanes_per_row in {4, 8, 16, 32}; steps_in_flight in {2, 4};
+ *   lanes_per_row in {4, 8, 16, 32}; steps_in_flight in {2, 4, 6};
  *   x_in_shared 0/1; ctas_per_sm >= 1 (0 = library default).
  * No counterpart in the reference (its launch shape is fixed,
  * kernels_torch_launchers.cuh:15-17).

@@ -457,7 +457,8 @@ int launch_d(int D, const void *values, const void *deltas, const int32_t *ri, i
     switch (D) {
         case 2: return launch<L, 1, XS>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
         case 4: return launch<L, 2, XS>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        default: return fail(MACKO_ERR_INVALID_ARGUMENT, "steps_in_flight must be 2 or 4 (got %d)", D);
+        case 6: return launch<L, 3, XS>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        default: return fail(MACKO_ERR_INVALID_ARGUMENT, "steps_in_flight must be 2, 4 or 6 (got %d)", D);
     }
 }
 
@@ -546,7 +547,8 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
     const long long avg_row = padded_count / rows;
     int L = rows >= 16384 ? 8 : 32;
     while (L > 4 && avg_row < (long long)L * kGroup / 2) L >>= 1;
-    const int D = avg_row > (long long)L * kGroup * 2 ? 4 : 2;
+    int D = avg_row > (long long)L * kGroup * 2 ? 4 : 2;
+    if (L == 8 && avg_row > (long long)L * kGroup * 6) D = 6;   // measured: 5-9 % faster than 4 with 8 lanes per row
     const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
     const bool xs = smem <= (size_t)dev->max_smem_optin;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

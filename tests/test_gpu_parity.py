@@ -140,7 +140,7 @@ def test_multiply_edge_shapes_all_kernel_shapes(shape):
         xd = x.to(_dev())
         _check_y(macko_spmv.multiply(comp, xd), comp_np, _u16(x), f"{shape} d={dens} default")
         for L in (4, 8, 16, 32):
-            for D in (2, 4):
+            for D in (2, 4, 6):
                 for xs in (0, 1):
                     if xs and cols > 100000:
                         continue
