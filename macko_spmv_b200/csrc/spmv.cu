@@ -424,11 +424,11 @@ int launch(const void *values, const void *deltas, const int32_t *ri, int rows, 
     }
     int per_sm = ctas_per_sm > 0 ? ctas_per_sm : 2;
     if (smem > 0) per_sm = max(1, min(per_sm, (int)((size_t)dev.max_smem_optin / (smem + 1024))));
-    // No more warps than row groups: a warp without rows would only stage x.
+    // Always a whole number of CTAs per SM: with fewer CTAs than that, some SMs would hold twice the rows
+    // of others. Only matrices with fewer row groups than CTAs get a smaller grid (one group per CTA).
     const long long groups = ((long long)rows * L + 31) / 32;
     long long ctas = (long long)dev.sm_count * per_sm;
-    const long long needed = (groups + kWarpsPerCta - 1) / kWarpsPerCta;
-    if (needed < ctas) ctas = needed < 1 ? 1 : needed;
+    if (groups < ctas) ctas = groups < 1 ? 1 : groups;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(kThreads);
