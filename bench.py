@@ -186,6 +186,92 @@ def per_case_numbers(cases, lib, peak_gbs):
     return out
 
 
+# --------------------------------------------------------------------------- large row-sharded matrices
+
+def sharded_large_leg(device, rank, world, lib, peer, peak_gbs, reps=40):
+    """The two large shapes (12288x49152, 49152x12288; Bernoulli masks at densities 0.1 and 0.5),
+    each rank holding a contiguous row block, the full y delivered to every rank. The four products
+    run back to back (together they stream more than L2 holds on every rank up to 8 GPUs), timed per
+    product with CUDA events, max over ranks. At one GPU the cuBLAS fp16 GEMV on the dense matrix is
+    timed beside each."""
+    import torch.distributed as dist
+
+    import macko_spmv_b200 as macko_spmv
+    from macko_spmv_b200 import cabi, sharded, workloads
+
+    cases = []
+    for si, (rows, cols) in enumerate(workloads.SHARDED_SHAPES):
+        for d in (0.1, 0.5):
+            seed = 7000 + 10 * si + int(round(d * 10))
+            M = workloads.bernoulli_matrix(rows, cols, d, seed, device=device, scale=0.02)
+            lo, hi = sharded.row_block(rows, rank, world)
+            block = M[lo:hi].contiguous()
+            del M
+            comp = macko_spmv.compress(block)
+            x = workloads.dense_vector(cols, seed + 500, device)
+            blocks = [sharded.row_block(rows, r, world) for r in range(world)]
+            gemv_us = None
+            if world == 1:
+                for _ in range(3):
+                    torch.mv(block, x)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(10):
+                    torch.mv(block, x)
+                e1.record()
+                torch.cuda.synchronize()
+                gemv_us = e0.elapsed_time(e1) * 100.0
+                ref = block.float() @ x.float()
+            cases.append({"rows": rows, "cols": cols, "density": d, "x": x, "gemv_us": gemv_us,
+                          "shard": sharded.RowShard(comp, lo, hi, rows, blocks),
+                          "y": torch.empty(rows, dtype=torch.float16, device=device) if world == 1 else None,
+                          "ref": ref if world == 1 else None,
+                          "bytes": workloads.algorithmic_bytes(comp[0].numel(), hi - lo, cols)})
+            del block
+    torch.cuda.empty_cache()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def product(c):
+        sh = c["shard"]
+        if peer is not None:
+            return peer.multiply(sh, c["x"])
+        comp = sh.compressed
+        cabi.check(lib, lib.macko_spmv_fp16(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4],
+                                            comp[0].numel(), c["x"].data_ptr(), c["y"].data_ptr(), 1.0, 0.0, stream))
+        if world > 1:
+            raise RuntimeError("sharded leg needs the peer exchange")
+        return c["y"]
+
+    for _ in range(3):
+        for c in cases:
+            product(c)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(cases) + 1)] for _ in range(reps)]
+    for r in range(reps):
+        marks[r][0].record()
+        for i, c in enumerate(cases):
+            product(c)
+            marks[r][i + 1].record()
+    torch.cuda.synchronize()
+    us = torch.tensor([[marks[r][i].elapsed_time(marks[r][i + 1]) * 1000.0 for i in range(len(cases))] for r in range(reps)],
+                      device=device).mean(dim=0)
+    if world > 1:
+        dist.all_reduce(us, op=dist.ReduceOp.MAX)
+    out = []
+    for c, t in zip(cases, us.tolist()):
+        row = {"shape": [c["rows"], c["cols"]], "density": c["density"], "us": round(t, 2),
+               "per_gpu_roofline_frac": round(c["bytes"] / (t * 1e-6) / 1e9 / peak_gbs, 4)}
+        if world == 1:
+            err = float((c["y"].float() - c["ref"]).norm() / c["ref"].norm())
+            assert err < 5e-3, f"large-matrix product is wrong (rel L2 {err})"
+            row["cublas_gemv_us"] = round(c["gemv_us"], 2)
+            row["speedup_vs_cublas"] = round(c["gemv_us"] / t, 3)
+        out.append(row)
+    return out
+
+
 # --------------------------------------------------------------------------- CPU reference path
 
 def cpu_reference_path(steps: int, warmup: int, gpu_cases=None):
@@ -317,7 +403,8 @@ def run_own_arm(args):
                                [sharded.row_block(c["rows"], r, world) for r in range(world)]) for c in cases]
     peer = None
     if world > 1 and args.exchange == "peer":
-        peer = sharded.PeerGather(max(c["rows"] for c in cases), device)
+        from macko_spmv_b200 import workloads
+        peer = sharded.PeerGather(max([c["rows"] for c in cases] + [r for r, _ in workloads.SHARDED_SHAPES]), device)
 
     def step_eager():
         stream = torch.cuda.current_stream().cuda_stream
@@ -413,6 +500,9 @@ def run_own_arm(args):
         assert err < 5e-3, f"timed kernel produced a wrong result (rel L2 {err})"
 
     per_case = per_case_numbers(cases, lib, peak_gbs) if (world == 1 and not args.no_per_case) else None
+    large = None
+    if not args.no_sharded_large and (world == 1 or peer is not None):
+        large = sharded_large_leg(device, rank, world, lib, peer, peak_gbs)
     cpu_base = cpu_reference_path(3, 1, gpu_cases=cases) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
 
     if rank == 0:
@@ -450,6 +540,11 @@ def run_own_arm(args):
         }
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
+        if large is not None:
+            line["sharded_large"] = {
+                "workload": "12288x49152 and 49152x12288, Bernoulli mask at densities 0.1 and 0.5, contiguous row block per GPU, "
+                            "full y on every rank; microseconds per product, max over ranks, products back to back",
+                "cases": large, "us_sum": round(sum(r["us"] for r in large), 2)}
         if per_case is not None:
             line["per_case"] = per_case
             sp = [p["speedup_vs_cublas"] for p in per_case]
@@ -500,6 +595,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-per-case", action="store_true", help="skip the per-matrix cuBLAS comparison")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sharded-large", action="store_true", help="skip the large row-sharded matrices")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how the y slices are exchanged (fused peer stores, or NCCL all-gather)")
     ap.add_argument("--single", default=None, metavar="ROWS,COLS,DENSITY",

@@ -177,14 +177,19 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         x_base = (int)__cvta_generic_to_shared(xs);
         __syncthreads();
     }
-    const int b2max = 2 * (kXPadFront + cols);
 
     // ---- per-group state ------------------------------------------------------------------------------
+    constexpr int LOG_STEP = (L == 32) ? 8 : (L == 16) ? 7 : (L == 8) ? 6 : 5;
     int my_row = -1;   // row being walked by my group (-1: none)
     int begin = 0;     // first stored element of the row
     int end = 0;       // one past the last stored element
     int pos = 0;       // first element of the group's next iteration (multiple of 8)
-    int sum2 = 0;      // 2 * (sum of the deltas of the row consumed so far)
+    // Byte address (shared window, or byte offset from x - kXPadFront when x stays in global memory) of
+    // "column -1 + index in row" in front of the lane's unit of the next sub-step, less 14 per lane below
+    // it in the group: the lane totals that go through the scan carry +14 each (see the decode below).
+    const unsigned lane_const = (unsigned)(x_base + 2 * kXPadFront + 2 * lig);
+    const unsigned a_max = (unsigned)(x_base + 2 * (kXPadFront + cols));
+    unsigned run = 0u;
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 
     for (;;) {
@@ -226,7 +231,8 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 const int e = min(__shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31), stored);
                 if (need) {
                     if (rank < take) {
-                        my_row = nr; begin = b; end = e; pos = b & ~(kGroup - 1); sum2 = 0;
+                        my_row = nr; begin = b; end = e; pos = b & ~(kGroup - 1);
+                        run = lane_const - 2u * (unsigned)(b & (kGroup - 1));   // the unit that holds `begin` starts before the row
                     } else {
                         my_row = -1; pos = 0; end = 0; begin = 0;
                     }
@@ -239,46 +245,55 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         uint4 v[D];
         unsigned w[D];
         const int ord0 = pos + lig * kGroup;
+        const int rem0 = end - ord0;    // elements of the row from the lane's first unit on
+        const int lo0 = begin - ord0;   // > 0: leading elements of sub-step 0 belong to the previous row
+        {
+            const uint4 *vp = values + (ord0 >> 3);
+            const unsigned *dp = deltas + (ord0 >> 3);
 #pragma unroll
-        for (int s = 0; s < D; ++s) {
-            const int ord = ord0 + s * STEP;
-            v[s] = make_uint4(0u, 0u, 0u, 0u);
-            w[s] = 0u;
-            if (ord < end) {
-                v[s] = ldg_stream_v4(values + (ord >> 3));
-                w[s] = ldg_stream_u32(deltas + (ord >> 3));
+            for (int s = 0; s < D; ++s) {
+                v[s] = make_uint4(0u, 0u, 0u, 0u);
+                w[s] = 0u;
+                if (s * STEP < rem0) {
+                    v[s] = ldg_stream_v4(vp + s * L);
+                    w[s] = ldg_stream_u32(dp + s * L);
+                }
             }
         }
-        const int lo0 = begin - ord0;   // > 0: leading elements of sub-step 0 belong to the previous row
-        const int rem0 = end - ord0;    // elements of the row from ord0 on
-        // byte offset (relative to the front padding) of "column -1 + index" before the lane's first element
-        int run = sum2 + 2 * (ord0 - begin) + 2 * kXPadFront;
+        // Which sub-steps hold a unit that straddles the first or the last element of a row, and how far the
+        // longest row of the warp still reaches: two warp-wide reductions per iteration replace a vote per unit.
+        unsigned mybits = 0u;
+        if (rem0 > 0) {
+            if (lo0 > 0) mybits = 1u;
+            const int tail = rem0 & (STEP - 1);
+            const unsigned s_end = (unsigned)rem0 >> LOG_STEP;
+            if (tail > 0 && tail < kGroup && s_end < (unsigned)D) mybits |= 1u << s_end;
+        }
+        const unsigned straddle = __reduce_or_sync(0xffffffffu, mybits);
+        const int max_rem = __reduce_max_sync(0xffffffffu, rem0);
 
 #pragma unroll
         for (int p = 0; p < NPAIR; ++p) {
             // a pair in which no lane of the warp has an element left ends the iteration
-            if (p > 0 && !__any_sync(0xffffffffu, rem0 > 2 * p * STEP)) break;
+            if (p > 0 && max_rem <= 2 * p * STEP) break;
             // Byte-SIMD prefix sums of the 8 deltas of a unit, scaled by 2 (byte offsets into fp16 x):
             //   ce byte j = 2*(inclusive prefix of element 2j)   + 2*(2j)
             //   co byte j = 2*(inclusive prefix of element 2j+1) + 2*(2j+1)
-            unsigned ce[2], co[2], t2[2];
+            // so the top byte of co is 2*(sum of the 8 deltas) + 14.
+            unsigned ce[2], co[2];
 #pragma unroll
             for (int hs = 0; hs < 2; ++hs) {
                 const int s = 2 * p + hs;
-                const int lo = (s == 0) ? lo0 : 0;
-                const int rem = rem0 - s * STEP;
-                // units that straddle the row's first or last element: only warps that have one pay
-                if (__any_sync(0xffffffffu, rem > 0 && (lo > 0 || rem < kGroup))) mask_unit(v[s], w[s], lo, rem);
-                const unsigned e2 = (w[s] << 1) & 0x1e1e1e1eu;
-                const unsigned o2 = (w[s] >> 3) & 0x1e1e1e1eu;
-                const unsigned pe = e2 * 0x01010101u;
-                const unsigned po = o2 * 0x01010101u;
-                ce[hs] = pe + (po << 8) + 0x0c080400u;
-                co[hs] = pe + po + 0x0e0a0602u;
-                t2[hs] = (pe + po) >> 24;
+                if (straddle & (1u << s)) mask_unit(v[s], w[s], (s == 0) ? lo0 : 0, rem0 - s * STEP);
+                const unsigned ev = w[s] & 0x0f0f0f0fu;
+                const unsigned od = (w[s] >> 4) & 0x0f0f0f0fu;
+                const unsigned pe = ev * 0x02020202u + 0x0c080400u;
+                const unsigned po = od * 0x02020202u;
+                ce[hs] = po * 256u + pe;
+                co[hs] = pe + po + 0x02020202u;
             }
             // one scan for both sub-steps: lane totals packed as two 16-bit fields (each < 2^13)
-            const unsigned t = t2[0] | (t2[1] << 16);
+            const unsigned t = (co[0] >> 24) | ((co[1] >> 8) & 0x00ff0000u);
             unsigned inc = t;
 #pragma unroll
             for (int o = 1; o < L; o <<= 1) {
@@ -290,36 +305,36 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
 #pragma unroll
             for (int hs = 0; hs < 2; ++hs) {
                 const int s = 2 * p + hs;
-                int b2 = run + (int)(hs ? (ex >> 16) : (ex & 0xffffu));
-                run += (int)(hs ? (g >> 16) : (g & 0xffffu)) + 2 * STEP;
-                b2 = min(max(b2, 0), b2max);   // keeps malformed input inside the padded x
+                // lane base = run + (low or high field of ex); the group advances by its field of g, which
+                // holds 14 per lane where 16 (2 bytes x 8 elements) are due: 2*L more per sub-step
+                const unsigned sel = hs ? 0x0100u : 0x0001u;
+                const unsigned a0 = min(__dp2a_lo(ex, sel, run) + (unsigned)(2 * L * s), a_max);   // keeps malformed input inside the padded x
+                run = __dp2a_lo(g, sel, run);
                 const unsigned *vw = reinterpret_cast<const unsigned *>(&v[s]);
                 unsigned xe[4], xo[4];
                 if (XS) {
-                    const int a0 = b2 + x_base;
-                    xe[0] = lds_u16((unsigned)add_byte<0>(ce[hs], a0));
-                    xo[0] = lds_u16((unsigned)add_byte<0>(co[hs], a0));
-                    xe[1] = lds_u16((unsigned)add_byte<1>(ce[hs], a0));
-                    xo[1] = lds_u16((unsigned)add_byte<1>(co[hs], a0));
-                    xe[2] = lds_u16((unsigned)add_byte<2>(ce[hs], a0));
-                    xo[2] = lds_u16((unsigned)add_byte<2>(co[hs], a0));
-                    xe[3] = lds_u16((unsigned)add_byte<3>(ce[hs], a0));
-                    xo[3] = lds_u16((unsigned)add_byte<3>(co[hs], a0));
+                    xe[0] = lds_u16((unsigned)add_byte<0>(ce[hs], (int)a0));
+                    xo[0] = lds_u16((unsigned)add_byte<0>(co[hs], (int)a0));
+                    xe[1] = lds_u16((unsigned)add_byte<1>(ce[hs], (int)a0));
+                    xo[1] = lds_u16((unsigned)add_byte<1>(co[hs], (int)a0));
+                    xe[2] = lds_u16((unsigned)add_byte<2>(ce[hs], (int)a0));
+                    xo[2] = lds_u16((unsigned)add_byte<2>(co[hs], (int)a0));
+                    xe[3] = lds_u16((unsigned)add_byte<3>(ce[hs], (int)a0));
+                    xo[3] = lds_u16((unsigned)add_byte<3>(co[hs], (int)a0));
                 } else {
                     const unsigned short *xg = reinterpret_cast<const unsigned short *>(x);
                     const int cmax = cols - 1;
-                    const int a0 = b2 - 2 * kXPadFront;
                     auto gather = [&](int off2) -> unsigned {
-                        return (unsigned)__ldg(xg + min(max(off2 >> 1, 0), cmax));
+                        return (unsigned)__ldg(xg + min(max((off2 >> 1) - kXPadFront, 0), cmax));
                     };
-                    xe[0] = gather(add_byte<0>(ce[hs], a0));
-                    xo[0] = gather(add_byte<0>(co[hs], a0));
-                    xe[1] = gather(add_byte<1>(ce[hs], a0));
-                    xo[1] = gather(add_byte<1>(co[hs], a0));
-                    xe[2] = gather(add_byte<2>(ce[hs], a0));
-                    xo[2] = gather(add_byte<2>(co[hs], a0));
-                    xe[3] = gather(add_byte<3>(ce[hs], a0));
-                    xo[3] = gather(add_byte<3>(co[hs], a0));
+                    xe[0] = gather(add_byte<0>(ce[hs], (int)a0));
+                    xo[0] = gather(add_byte<0>(co[hs], (int)a0));
+                    xe[1] = gather(add_byte<1>(ce[hs], (int)a0));
+                    xo[1] = gather(add_byte<1>(co[hs], (int)a0));
+                    xe[2] = gather(add_byte<2>(ce[hs], (int)a0));
+                    xo[2] = gather(add_byte<2>(co[hs], (int)a0));
+                    xe[3] = gather(add_byte<3>(ce[hs], (int)a0));
+                    xo[3] = gather(add_byte<3>(co[hs], (int)a0));
                 }
                 acc0 = fma_h<0>(acc0, vw[0], xe[0]);
                 acc1 = fma_h<1>(acc1, vw[0], xo[0]);
@@ -331,8 +346,8 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 acc3 = fma_h<1>(acc3, vw[3], xo[3]);
             }
         }
-        // delta sum consumed up to the end of the iteration (meaningless once the row is over)
-        sum2 = run - 2 * (ord0 + D * STEP - begin) - 2 * kXPadFront;
+        // every sub-step that was skipped lies behind the end of all rows of the warp: `run` is not used again before the next row resets it
+        run += (unsigned)(2 * L * D);
         pos += D * STEP;
     }
 

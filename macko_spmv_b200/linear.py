@@ -78,6 +78,39 @@ class MackoLinear(nn.Module):
                 f"stored={stored} ({2.5 * stored / max(2 * dense, 1):.3f} of dense bytes)")
 
 
+class RowShardedMackoLinear(nn.Module):
+    """Tensor-parallel `MackoLinear`: this rank holds a contiguous block of output features (rows of W)
+    in MACKO form; `forward` returns the full output on every rank.
+
+    The product and the exchange are one kernel (`sharded.PeerGather`). The returned tensor is a view of
+    one of the exchange's two slots: it must be consumed (in stream order) before the second-next
+    product issued through the same `PeerGather`; the decode loop in `llama_decode` does exactly that.
+    The reference has no multi-GPU layer; this is the layer its `fix()` would install under tensor
+    parallelism."""
+
+    def __init__(self, weight_block: torch.Tensor, row_lo: int, total_rows: int, peer):
+        super().__init__()
+        from . import compress, sharded
+
+        world = peer.world
+        blocks = [sharded.row_block(total_rows, r, world) for r in range(world)]
+        lo, hi = blocks[peer.rank]
+        if lo != row_lo or weight_block.size(0) != hi - lo:
+            raise ValueError(f"rank {peer.rank} must hold rows [{lo}, {hi}) of {total_rows}")
+        values, deltas, row_indices, rows, cols = compress(weight_block.contiguous())
+        self.register_buffer("c_0", values)
+        self.register_buffer("c_1", deltas)
+        self.register_buffer("c_2", row_indices)
+        self.out_features, self.in_features = int(total_rows), int(cols)
+        self.peer = peer
+        self.shard = sharded.RowShard((values, deltas, row_indices, rows, cols), lo, hi, total_rows, blocks, peer.group)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dim() != 1 or x.shape[0] != self.in_features:
+            raise RuntimeError(f"expected a vector of {self.in_features} elements, got {tuple(x.shape)}")
+        return self.peer.multiply(self.shard, x.contiguous())
+
+
 def compress_state_dict(state_dict, select=lambda name: ("self_attn" in name or "mlp" in name) and name.endswith(".weight")):
     """Replace every selected 2-D fp16 `<name>.weight` by `<name>.c_0 … c_4`.
 

@@ -9,25 +9,42 @@ the GPU, and decodes greedily with one captured CUDA graph per token. Prompt tok
 same single-token step. It is a caller of the hot path, used to report tokens/s; it is not a model zoo.
 
     python -m macko_spmv_b200.llama_decode --density 0.5 --layers 32
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m macko_spmv_b200.llama_decode --density 0.5
+
+Tensor parallel (one process per GPU): every linear layer is split by output features into contiguous
+row blocks; each SpMV kernel stores its slice of y into every rank's copy over NVLink and ends when all
+slices have arrived (`RowShardedMackoLinear`), so a token costs 4 fused product+exchange kernels per
+block and no collective call. Norms, rotary embedding, the KV cache and attention are replicated: at
+batch 1 attention over a few hundred positions takes microseconds, less than one more exchange would.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
+import sys
 import time
 
 import torch
 from torch import nn
 
 from . import compress, workloads
-from .linear import MackoLinear
+from .linear import MackoLinear, RowShardedMackoLinear
 
 LLAMA2_7B = dict(hidden=4096, heads=32, ffn=11008, vocab=32000, layers=32, eps=1e-5, rope_theta=10000.0)
 
 
-def _pruned_linear(out_features: int, in_features: int, density: float, seed: int, device) -> nn.Module:
-    """A MackoLinear (density < 1) or a dense nn.Linear (density >= 1, the cuBLAS baseline)."""
+def _pruned_linear(out_features: int, in_features: int, density: float, seed: int, device, peer=None) -> nn.Module:
+    """A MackoLinear (density < 1) or a dense nn.Linear (density >= 1, the cuBLAS baseline); with `peer`
+    (a `sharded.PeerGather`) this rank's row block as a RowShardedMackoLinear."""
     w = workloads.magnitude_pruned_matrix(out_features, in_features, min(density, 1.0), seed, device=device)
+    if peer is not None:
+        if density >= 1.0:
+            raise ValueError("the tensor-parallel path runs MACKO layers only (density < 1)")
+        from .sharded import row_block
+
+        lo, hi = row_block(out_features, peer.rank, peer.world)
+        return RowShardedMackoLinear(w[lo:hi], lo, out_features, peer)
     if density >= 1.0:
         lin = nn.Linear(in_features, out_features, bias=False, device=device, dtype=torch.float16)
         with torch.no_grad():
@@ -51,16 +68,16 @@ class Block(nn.Module):
     """One transformer block. q/k/v and gate/up are stored as one matrix each (rows concatenated), so a
     token costs four SpMVs per block; the glue around them is kept to a handful of kernels."""
 
-    def __init__(self, cfg, density, seed, device, max_len):
+    def __init__(self, cfg, density, seed, device, max_len, peer=None):
         super().__init__()
         h, f = cfg["hidden"], cfg["ffn"]
         self.heads = cfg["heads"]
         self.head_dim = h // self.heads
         self.hidden, self.ffn = h, f
-        self.qkv_proj = _pruned_linear(3 * h, h, density, seed + 0, device)
-        self.o_proj = _pruned_linear(h, h, density, seed + 3, device)
-        self.gate_up_proj = _pruned_linear(2 * f, h, density, seed + 4, device)
-        self.down_proj = _pruned_linear(h, f, density, seed + 6, device)
+        self.qkv_proj = _pruned_linear(3 * h, h, density, seed + 0, device, peer)
+        self.o_proj = _pruned_linear(h, h, density, seed + 3, device, peer)
+        self.gate_up_proj = _pruned_linear(2 * f, h, density, seed + 4, device, peer)
+        self.down_proj = _pruned_linear(h, f, density, seed + 6, device, peer)
         self.input_norm = RMSNorm(h, cfg["eps"], device)
         self.post_norm = RMSNorm(h, cfg["eps"], device)
         self.register_buffer("k_cache", torch.zeros(1, self.heads, max_len, self.head_dim, dtype=torch.float16, device=device))
@@ -88,7 +105,7 @@ def _rope(t, cos, sin):
 
 class LlamaDecoder(nn.Module):
     def __init__(self, density: float, cfg=None, layers=None, device="cuda", max_len=384, seed=4000,
-                 prune_lm_head=True):
+                 prune_lm_head=True, peer=None):
         super().__init__()
         cfg = dict(LLAMA2_7B if cfg is None else cfg)
         if layers is not None:
@@ -97,9 +114,10 @@ class LlamaDecoder(nn.Module):
         h = cfg["hidden"]
         g = torch.Generator(device=device).manual_seed(seed)
         self.embed = (0.02 * torch.randn(cfg["vocab"], h, generator=g, device=device)).to(torch.float16)
-        self.blocks = nn.ModuleList([Block(cfg, density, seed + 100 * (i + 1), device, max_len) for i in range(cfg["layers"])])
+        self.blocks = nn.ModuleList([Block(cfg, density, seed + 100 * (i + 1), device, max_len, peer) for i in range(cfg["layers"])])
         self.norm = RMSNorm(h, cfg["eps"], device)
-        self.lm_head = _pruned_linear(cfg["vocab"], h, density if prune_lm_head else 1.0, seed + 7, device)
+        self.lm_head = _pruned_linear(cfg["vocab"], h, density if prune_lm_head else 1.0, seed + 7, device,
+                                      peer if prune_lm_head else None)
         half = (h // cfg["heads"]) // 2
         inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(half, device=device, dtype=torch.float32) / half))
         ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
@@ -111,14 +129,17 @@ class LlamaDecoder(nn.Module):
 
     def step(self, token, pos):
         """token int64[1], pos int64[1] (device tensors) -> next token int64[1] (greedy)."""
+        return torch.argmax(self.logits(token, pos).float(), dim=-1, keepdim=True)
+
+    def logits(self, token, pos):
+        """fp16 logits [vocab] of the token at position `pos`; updates the KV cache."""
         x = self.embed.index_select(0, token)[0]
         cos = self.cos_table.index_select(0, pos)[0]
         sin = self.sin_table.index_select(0, pos)[0]
         mask = torch.where(self.positions <= pos, self.zero, self.neg_inf).view(1, 1, 1, -1)
         for blk in self.blocks:
             x = blk(x, pos, cos, sin, mask)
-        logits = self.lm_head(self.norm(x))
-        return torch.argmax(logits.float(), dim=-1, keepdim=True)
+        return self.lm_head(self.norm(x))
 
 
 @torch.no_grad()
@@ -176,23 +197,59 @@ def main():
     ap.add_argument("--dense-lm-head", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
-    torch.cuda.set_device(0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    peer = None
+    if world > 1:
+        import torch.distributed as dist
+
+        from .sharded import PeerGather
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.pop("NCCL_DEBUG", None)
+        dist.init_process_group("nccl", device_id=device)
+        cfg = LLAMA2_7B
+        peer = PeerGather(max(3 * cfg["hidden"], 2 * cfg["ffn"], cfg["vocab"]), device)
     t0 = time.perf_counter()
-    model = LlamaDecoder(args.density, layers=args.layers, max_len=args.prompt + args.new_tokens,
-                         prune_lm_head=not args.dense_lm_head)
+    model = LlamaDecoder(args.density, layers=args.layers, device=device, max_len=args.prompt + args.new_tokens,
+                         prune_lm_head=not args.dense_lm_head, peer=peer)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
-    g = torch.Generator(device="cuda").manual_seed(4001)
-    prompt = torch.randint(0, model.cfg["vocab"], (args.prompt,), generator=g, device="cuda")
-    _, gen_s, prompt_s = generate(model, prompt, args.new_tokens, use_graph=not args.no_graph)
-    print(json.dumps({
-        "model": "llama-2-7b architecture, random init", "layers": args.layers, "density": args.density,
-        "lm_head": "dense" if args.dense_lm_head or args.density >= 1 else "pruned",
-        "prompt_tokens": args.prompt, "new_tokens": args.new_tokens,
-        "tokens_per_s": args.new_tokens / gen_s, "prompt_tokens_per_s": args.prompt / prompt_s,
-        "build_seconds": build_s, "memory_GB": torch.cuda.max_memory_allocated() / 1e9,
-        "cuda_graph": not args.no_graph,
-    }), flush=True)
+    g = torch.Generator(device=device).manual_seed(4001)
+    prompt = torch.randint(0, model.cfg["vocab"], (args.prompt,), generator=g, device=device)
+    if world > 1:
+        dist.barrier()
+    tokens, gen_s, prompt_s = generate(model, prompt, args.new_tokens, use_graph=not args.no_graph)
+    same = True
+    if world > 1:
+        t = torch.tensor([gen_s, prompt_s], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gen_s, prompt_s = float(t[0]), float(t[1])
+        ref = tokens.clone()
+        dist.broadcast(ref, 0)
+        agree = torch.tensor([int(torch.equal(ref, tokens))], device=device)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        same = bool(agree.item()) and peer.error_flag() == 0
+    if rank == 0:
+        print(json.dumps({
+            "model": "llama-2-7b architecture, random init", "layers": args.layers, "density": args.density,
+            "tensor_parallel": world, "ranks_agree": same,
+            "lm_head": "dense" if args.dense_lm_head or args.density >= 1 else "pruned",
+            "prompt_tokens": args.prompt, "new_tokens": args.new_tokens,
+            "tokens_per_s": args.new_tokens / gen_s, "prompt_tokens_per_s": args.prompt / prompt_s,
+            "build_seconds": build_s, "memory_GB": torch.cuda.max_memory_allocated() / 1e9,
+            "cuda_graph": not args.no_graph, "first_tokens": tokens[:8].tolist(),
+        }), flush=True)
+    if world > 1:
+        # leave without tearing the communicator down while a captured graph still references it
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -54,11 +54,52 @@ def _worker(rank, world, port, q):
     os._exit(0)   # skip NCCL teardown, as bench.py does
 
 
-def _run(world):
+def _decode_worker(rank, world, port, q):
+    """A small Llama-architecture decoder, tensor parallel over `world` ranks, against the same model on
+    one GPU: logits within tolerance of each other and bit-identical on every rank."""
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    ok, msg = True, ""
+    try:
+        from macko_spmv_b200 import llama_decode, sharded
+
+        cfg = dict(hidden=256, heads=4, ffn=688, vocab=1000, layers=2, eps=1e-5, rope_theta=10000.0)
+        pg = sharded.PeerGather(max(3 * 256, 2 * 688, 1000), dev)
+        with torch.no_grad():
+            tp = llama_decode.LlamaDecoder(0.5, cfg=cfg, device=dev, max_len=16, seed=123, peer=pg)
+            one = llama_decode.LlamaDecoder(0.5, cfg=cfg, device=dev, max_len=16, seed=123)
+            for i, tok in enumerate([5, 999, 0, 421]):
+                token = torch.tensor([tok], device=dev)
+                pos = torch.tensor([i], device=dev)
+                a = tp.logits(token, pos).clone()
+                b = one.logits(token, pos)
+                rel = float((a.float() - b.float()).norm() / b.float().norm())
+                ref = a.clone()
+                dist.broadcast(ref, 0)
+                if rel > 1e-2 or not torch.equal(ref, a):
+                    ok, msg = False, f"rank {rank}: token {i} rel {rel} same_on_ranks {torch.equal(ref, a)}"
+        if pg.error_flag() != 0:
+            ok, msg = False, f"rank {rank}: wait gave up on rank {pg.error_flag() - 1}"
+    except Exception as e:  # noqa: BLE001
+        ok, msg = False, f"rank {rank}: {type(e).__name__}: {e}"
+    q.put((rank, ok, msg))
+    torch.cuda.synchronize()
+    dist.barrier()
+    os._exit(0)
+
+
+def _run(world, target=None):
+    target = target or _worker
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=target, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=240) for _ in range(world)]
@@ -74,3 +115,12 @@ def test_fused_exchange_world_1():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_exchange_world_2():
     _run(2)
+
+
+def test_tensor_parallel_decode_world_1():
+    _run(1, _decode_worker)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_decode_world_2():
+    _run(2, _decode_worker)
