@@ -81,6 +81,33 @@ int macko_spmv_fp16_tuned(const void *values, const void *deltas, const int32_t 
                           int lanes_per_row, int steps_in_flight, int x_in_shared, int ctas_per_sm);
 
 /*
+ * Y = alpha * M X + beta * Y for `batch` right-hand sides at once: x is [batch][cols] and y is
+ * [batch][rows], both row-major fp16 (the layout of a [tokens, features] activation). Up to 8 vectors
+ * share one pass over the compressed matrix (their values are interleaved in shared memory so that one
+ * vector load gathers a column of all of them); larger batches run in chunks of 8, and fewer vectors per
+ * pass are used when `cols` is too large for that many copies of x in shared memory. Every vector
+ * gets the result of macko_spmv_fp16 up to the order of the fp32 additions.
+ *
+ * Replaces the loop of single-vector launches that the reference runs for batched inputs through
+ * torch.vmap (python_scripts/util_run_pruned_llm.py:112-115; the reference kernel is built for
+ * BATCH = 1, c_benchmarking/utils.cuh:299).
+ */
+int macko_spmm_fp16(const void *values, const void *deltas, const int32_t *row_indices,
+                    int64_t rows, int64_t cols, int64_t padded_count,
+                    const void *x, void *y, int64_t batch, float alpha, float beta, void *stream);
+
+/*
+ * Dense row-major fp16 [rows][cols] from a compressed matrix: element k of a row goes to column
+ * (sum of the deltas of elements 0..k) + k, as the reference kernel decodes it
+ * (src/macko_spmv/cuda/kernels.cuh:86-108); stored non-zeros keep their bits, everything else
+ * (pads included) is +0. `dense` (rows * cols * 2 bytes) is written exactly once, on `stream` (16-byte stores when it is 16-byte aligned). The reference has no
+ * decompressor; this one serves products with many right-hand sides (dense copy + GEMM) and round-trip
+ * checks of the compressor.
+ */
+int macko_decompress_fp16(const void *values, const void *deltas, const int32_t *row_indices,
+                          int64_t rows, int64_t cols, int64_t padded_count, void *dense, void *stream);
+
+/*
  * GPU compressor, phase 1: per-row stored-element counts and their prefix sum.
  *
  * Replaces (together with macko_compress_emit): `compress_rows_cpu`

@@ -37,7 +37,7 @@ def _load_native():
         if not os.path.exists(path):
             raise ImportError(
                 f"{path} is missing: build the native libraries first with "
-                "`python -m macko_spmv_b200.build` (needs nvcc and g++)."
+                "`python macko_spmv_b200/build.py` (needs nvcc and g++)."
             )
     core = ctypes.CDLL(_CORE_PATH, mode=ctypes.RTLD_GLOBAL)
     torch.ops.load_library(_OPS_PATH)
@@ -74,6 +74,16 @@ def _compress_fake(M):
         M.new_empty((n * 4,), dtype=torch.uint8),
         M.new_empty((M.shape[0] + 1,), dtype=torch.int32),
     )
+
+
+@torch.library.register_fake("macko_spmv::multiply_batched")
+def _multiply_batched_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, V):
+    return torch.empty((V.shape[0], M_rows), device=M_values.device, dtype=M_values.dtype)
+
+
+@torch.library.register_fake("macko_spmv::decompress")
+def _decompress_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols):
+    return torch.empty((M_rows, M_cols), device=M_values.device, dtype=M_values.dtype)
 
 
 def move_to_device(compressed, device):
@@ -125,4 +135,32 @@ def multiply(compressed_M, V):
     )
 
 
-__all__ = ["compress", "multiply", "move_to_device", "native_library_paths", "native_version", "LIB_NAME"]
+# Above this many right-hand sides a dense copy of the matrix plus one tensor-core GEMM is cheaper than
+# streaming the compressed matrix once per 8 vectors.
+DENSE_BATCH_THRESHOLD = 16
+
+
+def decompress(compressed_M):
+    """Dense fp16 [rows, cols] of a compressed CUDA matrix (every zero, pads included, comes back as +0)."""
+    assert compressed_M[0].is_cuda
+    return torch.ops.macko_spmv.decompress.default(*compressed_M[:5])
+
+
+def multiply_batched(compressed_M, V):
+    """Y[batch, rows] = V[batch, cols] @ M^T for a compressed matrix and fp16 CUDA vectors.
+
+    The reference runs batched inputs as a loop of `multiply` calls (torch.vmap fallback,
+    python_scripts/util_run_pruned_llm.py:112-115). Here 2..DENSE_BATCH_THRESHOLD vectors share passes
+    over the compressed matrix (8 per pass); larger batches decompress once and run a dense GEMM.
+    """
+    assert compressed_M[0].is_cuda
+    assert V.is_cuda
+    assert V.is_contiguous()
+    if V.dim() != 2:
+        raise RuntimeError("V must have shape [batch, cols]")
+    if V.shape[0] > DENSE_BATCH_THRESHOLD:
+        return V @ decompress(compressed_M).t()
+    return torch.ops.macko_spmv.multiply_batched.default(*compressed_M[:5], V)
+
+
+__all__ = ["compress", "multiply", "multiply_batched", "decompress", "move_to_device", "native_library_paths", "native_version", "LIB_NAME"]

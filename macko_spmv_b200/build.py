@@ -3,7 +3,7 @@
 ``libmacko_b200.so``  CUDA kernels + C ABI (nvcc, sm_100a only, no torch dependency)
 ``_torch_ops.so``     the `macko_spmv::*` torch operators, linked against the C ABI
 
-Run ``python -m macko_spmv_b200.build`` (or call :func:`build`). Nothing is compiled at
+Run ``python macko_spmv_b200/build.py`` (or call :func:`build`). Nothing is compiled at
 import time; importing the package without the built libraries raises.
 """
 from __future__ import annotations
@@ -19,7 +19,7 @@ INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_CORE = os.path.join(PKG_DIR, "libmacko_b200.so")
 LIB_TORCH = os.path.join(PKG_DIR, "_torch_ops.so")
 
-CUDA_SOURCES = ["common.cu", "spmv.cu", "compress.cu"]
+CUDA_SOURCES = ["common.cu", "spmv.cu", "compress.cu", "decompress.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

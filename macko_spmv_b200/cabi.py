@@ -30,6 +30,8 @@ SIGNATURES = {
     "macko_last_error": (ctypes.c_char_p, []),
     "macko_spmv_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp]),
     "macko_spmv_fp16_tuned": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp, _int, _int, _int, _int]),
+    "macko_spmm_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _f, _f, _vp]),
+    "macko_decompress_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "macko_compress_count": (_int, [_vp, _i64, _i64, _vp, _vp]),
     "macko_compress_workspace_bytes": (_i64, [_i64]),
     "macko_compress_emit": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
@@ -49,7 +51,7 @@ class MackoError(RuntimeError):
 def load(path: str = LIB_PATH) -> ctypes.CDLL:
     """Load the C-ABI library and attach the signatures above."""
     if not os.path.exists(path):
-        raise ImportError(f"{path} is missing: run `python -m macko_spmv_b200.build`")
+        raise ImportError(f"{path} is missing: run `python macko_spmv_b200/build.py`")
     lib = ctypes.CDLL(path)
     for name, (restype, argtypes) in SIGNATURES.items():
         fn = getattr(lib, name)

@@ -53,6 +53,33 @@ __device__ __forceinline__ float fma_h(float acc, unsigned vword, unsigned xbits
     return acc;
 }
 
+// acc += fp16(half VH of vword) * fp16(half XH of xword)
+template <int VH, int XH>
+__device__ __forceinline__ float fma_hh(float acc, unsigned vword, unsigned xword)
+{
+    if (VH == 0 && XH == 0)
+        asm("{.reg .b16 vl,vh,xl,xh; mov.b32 {vl,vh}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, vl, xl, %0;}" : "+f"(acc) : "r"(vword), "r"(xword));
+    else if (VH == 0 && XH == 1)
+        asm("{.reg .b16 vl,vh,xl,xh; mov.b32 {vl,vh}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, vl, xh, %0;}" : "+f"(acc) : "r"(vword), "r"(xword));
+    else if (VH == 1 && XH == 0)
+        asm("{.reg .b16 vl,vh,xl,xh; mov.b32 {vl,vh}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, vh, xl, %0;}" : "+f"(acc) : "r"(vword), "r"(xword));
+    else
+        asm("{.reg .b16 vl,vh,xl,xh; mov.b32 {vl,vh}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, vh, xh, %0;}" : "+f"(acc) : "r"(vword), "r"(xword));
+    return acc;
+}
+
+// BV consecutive fp16 values (BV = 2, 4 or 8) from shared memory into BV/2 words
+template <int BV>
+__device__ __forceinline__ void lds_vec(unsigned addr, unsigned (&r)[BV / 2])
+{
+    if constexpr (BV == 2)
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r[0]) : "r"(addr));
+    else if constexpr (BV == 4)
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+    else
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
 __device__ __forceinline__ uint4 ldg_stream_v4(const uint4 *p)
 {
     uint4 r;
@@ -77,10 +104,10 @@ __device__ __forceinline__ unsigned lds_u16(unsigned addr)
 
 // c + byte `J` of a: one integer dot-product instruction extracts the byte and adds the base, and it
 // does not run on the (half-rate) integer ALU pipe the rest of the index arithmetic competes for.
-template <int J>
+template <int J, int M = 1>
 __device__ __forceinline__ int add_byte(unsigned a, int c)
 {
-    return __dp4a(a, 1u << (8 * J), (unsigned)c);
+    return __dp4a(a, (unsigned)M << (8 * J), (unsigned)c);   // c + M * byte J of a
 }
 
 // Zero the deltas and the fp16 values of one 8-element unit outside element range [lo, hi).
@@ -102,6 +129,8 @@ __device__ __forceinline__ void mask_unit(uint4 &v, unsigned &w, int lo, int hi)
 
 // Where a row-sharded launch delivers its slice of y: the full-y buffer of every rank (peer-mapped
 // device pointers) and every rank's flag words. world == 0 for an ordinary launch.
+template <int V> struct Int { static constexpr int value = V; };
+
 constexpr int kMaxPeers = 8;
 struct Peers {
     __half *y[kMaxPeers];
@@ -117,12 +146,16 @@ struct Peers {
 // XS    x staged in shared memory (else gathered from global memory with explicit clamping)
 // PEER  the epilogue stores every y value into the full-y buffer of all ranks over NVLink and, once the
 //       whole grid is done, bumps this rank's arrival counter on every rank (no collective call follows)
-template <int L, int NPAIR, bool XS, bool PEER>
+// BV    vectors multiplied at once (1, 2, 4 or 8): x is [batch][cols] and y is [batch][rows], batch <= BV.
+//       The matrix is streamed once; shared memory holds the vectors interleaved (BV values per column),
+//       so one vector load gathers a column of all of them.
+template <int L, int NPAIR, bool XS, bool PEER, int BV = 1>
 __global__ void __launch_bounds__(kThreads, 2)
 spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
             const int *__restrict__ ri, const __half *__restrict__ x, __half *__restrict__ y,
-            int rows, int cols, int stored, float alpha, float beta, const Peers peers)
+            int rows, int cols, int stored, float alpha, float beta, const Peers peers, int batch)
 {
+    static_assert(BV == 1 || (XS && !PEER), "batched products gather from shared memory and have no scatter epilogue");
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int STEP = kGroup * L;   // elements per group per sub-step
     constexpr int D = 2 * NPAIR;       // sub-steps per iteration
@@ -160,7 +193,20 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
 
     // ---- stage x into shared memory, framed by zeros ------------------------------------------------
     int x_base = 0;  // shared-window byte address of the front padding
-    if (XS) {
+    if (BV > 1) {
+        __half *xs = reinterpret_cast<__half *>(smem);
+        const int n_total = (kXPadFront + cols + kXPadBack) * BV;
+        for (int i = tid; i < kXPadFront * BV; i += kThreads) xs[i] = __ushort_as_half(0);
+        for (int i = (kXPadFront + cols) * BV + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
+#pragma unroll
+        for (int b = 0; b < BV; ++b) {
+            const __half *xb = x + (size_t)b * cols;
+            for (int c = tid; c < cols; c += kThreads)
+                xs[(size_t)(kXPadFront + c) * BV + b] = b < batch ? xb[c] : __ushort_as_half(0);
+        }
+        x_base = (int)__cvta_generic_to_shared(xs);
+        __syncthreads();
+    } else if (XS) {
         __half *xs = reinterpret_cast<__half *>(smem);
         const int n_total = kXPadFront + cols + kXPadBack;
         for (int i = tid; i < kXPadFront; i += kThreads) xs[i] = __ushort_as_half(0);
@@ -187,30 +233,52 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     // Byte address (shared window, or byte offset from x - kXPadFront when x stays in global memory) of
     // "column -1 + index in row" in front of the lane's unit of the next sub-step, less 14 per lane below
     // it in the group: the lane totals that go through the scan carry +14 each (see the decode below).
-    const unsigned lane_const = (unsigned)(x_base + 2 * kXPadFront + 2 * lig);
-    const unsigned a_max = (unsigned)(x_base + 2 * (kXPadFront + cols));
+    const int x_fold = (BV == 1) ? x_base : 0;   // batched: offsets stay per-vector and are scaled by BV at the gather
+    const unsigned lane_const = (unsigned)(x_fold + 2 * kXPadFront + 2 * lig);
+    const unsigned a_max = (unsigned)(x_fold + 2 * (kXPadFront + cols));
     unsigned run = 0u;
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    float accb[BV][2];   // batched: per vector, even and odd elements
+#pragma unroll
+    for (int b = 0; b < BV; ++b) accb[b][0] = accb[b][1] = 0.f;
 
     for (;;) {
         // ---- groups that ran out of work finish their row and take the next one ---------------------
         const bool need = pos >= end;
         const unsigned needmask = __ballot_sync(0xffffffffu, need);
         if (needmask) {
-            float total = (acc0 + acc1) + (acc2 + acc3);
+            if constexpr (BV == 1) {
+                float total = (acc0 + acc1) + (acc2 + acc3);
 #pragma unroll
-            for (int o = L / 2; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-            if (need) {
-                if (my_row >= 0 && lig == 0) {
-                    float r = alpha * total;
-                    if (PEER) {
-                        ystage[my_row - cta_row_lo] = __float2half_rn(r);   // delivered in bulk at the end
-                    } else {
-                        if (beta != 0.f) r += beta * __half2float(y[my_row]);
-                        y[my_row] = __float2half_rn(r);
+                for (int o = L / 2; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                if (need) {
+                    if (my_row >= 0 && lig == 0) {
+                        float r = alpha * total;
+                        if (PEER) {
+                            ystage[my_row - cta_row_lo] = __float2half_rn(r);   // delivered in bulk at the end
+                        } else {
+                            if (beta != 0.f) r += beta * __half2float(y[my_row]);
+                            y[my_row] = __float2half_rn(r);
+                        }
+                    }
+                    acc0 = acc1 = acc2 = acc3 = 0.f;
+                }
+            } else {
+#pragma unroll
+                for (int b = 0; b < BV; ++b) {
+                    float total = accb[b][0] + accb[b][1];
+#pragma unroll
+                    for (int o = L / 2; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                    if (need) {
+                        if (my_row >= 0 && lig == 0 && b < batch) {
+                            __half *yb = y + (size_t)b * rows;
+                            float r = alpha * total;
+                            if (beta != 0.f) r += beta * __half2float(yb[my_row]);
+                            yb[my_row] = __float2half_rn(r);
+                        }
+                        accb[b][0] = accb[b][1] = 0.f;
                     }
                 }
-                acc0 = acc1 = acc2 = acc3 = 0.f;
             }
             const int avail = row_hi - row_next;
             if (avail <= 0) {
@@ -311,39 +379,60 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 const unsigned a0 = min(__dp2a_lo(ex, sel, run) + (unsigned)(2 * L * s), a_max);   // keeps malformed input inside the padded x
                 run = __dp2a_lo(g, sel, run);
                 const unsigned *vw = reinterpret_cast<const unsigned *>(&v[s]);
-                unsigned xe[4], xo[4];
-                if (XS) {
-                    xe[0] = lds_u16((unsigned)add_byte<0>(ce[hs], (int)a0));
-                    xo[0] = lds_u16((unsigned)add_byte<0>(co[hs], (int)a0));
-                    xe[1] = lds_u16((unsigned)add_byte<1>(ce[hs], (int)a0));
-                    xo[1] = lds_u16((unsigned)add_byte<1>(co[hs], (int)a0));
-                    xe[2] = lds_u16((unsigned)add_byte<2>(ce[hs], (int)a0));
-                    xo[2] = lds_u16((unsigned)add_byte<2>(co[hs], (int)a0));
-                    xe[3] = lds_u16((unsigned)add_byte<3>(ce[hs], (int)a0));
-                    xo[3] = lds_u16((unsigned)add_byte<3>(co[hs], (int)a0));
-                } else {
-                    const unsigned short *xg = reinterpret_cast<const unsigned short *>(x);
-                    const int cmax = cols - 1;
-                    auto gather = [&](int off2) -> unsigned {
-                        return (unsigned)__ldg(xg + min(max((off2 >> 1) - kXPadFront, 0), cmax));
+                if constexpr (BV > 1) {
+                    const int ab = x_base + (int)a0 * BV;
+                    auto element_pair = [&](auto jt) {
+                        constexpr int J = decltype(jt)::value;
+                        unsigned xe[BV / 2], xo[BV / 2];
+                        lds_vec<BV>((unsigned)add_byte<J, BV>(ce[hs], ab), xe);
+                        lds_vec<BV>((unsigned)add_byte<J, BV>(co[hs], ab), xo);
+#pragma unroll
+                        for (int b = 0; b < BV; b += 2) {
+                            accb[b][0] = fma_hh<0, 0>(accb[b][0], vw[J], xe[b / 2]);
+                            accb[b + 1][0] = fma_hh<0, 1>(accb[b + 1][0], vw[J], xe[b / 2]);
+                            accb[b][1] = fma_hh<1, 0>(accb[b][1], vw[J], xo[b / 2]);
+                            accb[b + 1][1] = fma_hh<1, 1>(accb[b + 1][1], vw[J], xo[b / 2]);
+                        }
                     };
-                    xe[0] = gather(add_byte<0>(ce[hs], (int)a0));
-                    xo[0] = gather(add_byte<0>(co[hs], (int)a0));
-                    xe[1] = gather(add_byte<1>(ce[hs], (int)a0));
-                    xo[1] = gather(add_byte<1>(co[hs], (int)a0));
-                    xe[2] = gather(add_byte<2>(ce[hs], (int)a0));
-                    xo[2] = gather(add_byte<2>(co[hs], (int)a0));
-                    xe[3] = gather(add_byte<3>(ce[hs], (int)a0));
-                    xo[3] = gather(add_byte<3>(co[hs], (int)a0));
+                    element_pair(Int<0>{});
+                    element_pair(Int<1>{});
+                    element_pair(Int<2>{});
+                    element_pair(Int<3>{});
+                } else {
+                    unsigned xe[4], xo[4];
+                    if (XS) {
+                        xe[0] = lds_u16((unsigned)add_byte<0>(ce[hs], (int)a0));
+                        xo[0] = lds_u16((unsigned)add_byte<0>(co[hs], (int)a0));
+                        xe[1] = lds_u16((unsigned)add_byte<1>(ce[hs], (int)a0));
+                        xo[1] = lds_u16((unsigned)add_byte<1>(co[hs], (int)a0));
+                        xe[2] = lds_u16((unsigned)add_byte<2>(ce[hs], (int)a0));
+                        xo[2] = lds_u16((unsigned)add_byte<2>(co[hs], (int)a0));
+                        xe[3] = lds_u16((unsigned)add_byte<3>(ce[hs], (int)a0));
+                        xo[3] = lds_u16((unsigned)add_byte<3>(co[hs], (int)a0));
+                    } else {
+                        const unsigned short *xg = reinterpret_cast<const unsigned short *>(x);
+                        const int cmax = cols - 1;
+                        auto gather = [&](int off2) -> unsigned {
+                            return (unsigned)__ldg(xg + min(max((off2 >> 1) - kXPadFront, 0), cmax));
+                        };
+                        xe[0] = gather(add_byte<0>(ce[hs], (int)a0));
+                        xo[0] = gather(add_byte<0>(co[hs], (int)a0));
+                        xe[1] = gather(add_byte<1>(ce[hs], (int)a0));
+                        xo[1] = gather(add_byte<1>(co[hs], (int)a0));
+                        xe[2] = gather(add_byte<2>(ce[hs], (int)a0));
+                        xo[2] = gather(add_byte<2>(co[hs], (int)a0));
+                        xe[3] = gather(add_byte<3>(ce[hs], (int)a0));
+                        xo[3] = gather(add_byte<3>(co[hs], (int)a0));
+                    }
+                    acc0 = fma_h<0>(acc0, vw[0], xe[0]);
+                    acc1 = fma_h<1>(acc1, vw[0], xo[0]);
+                    acc2 = fma_h<0>(acc2, vw[1], xe[1]);
+                    acc3 = fma_h<1>(acc3, vw[1], xo[1]);
+                    acc0 = fma_h<0>(acc0, vw[2], xe[2]);
+                    acc1 = fma_h<1>(acc1, vw[2], xo[2]);
+                    acc2 = fma_h<0>(acc2, vw[3], xe[3]);
+                    acc3 = fma_h<1>(acc3, vw[3], xo[3]);
                 }
-                acc0 = fma_h<0>(acc0, vw[0], xe[0]);
-                acc1 = fma_h<1>(acc1, vw[0], xo[0]);
-                acc2 = fma_h<0>(acc2, vw[1], xe[1]);
-                acc3 = fma_h<1>(acc3, vw[1], xo[1]);
-                acc0 = fma_h<0>(acc0, vw[2], xe[2]);
-                acc1 = fma_h<1>(acc1, vw[2], xo[2]);
-                acc2 = fma_h<0>(acc2, vw[3], xe[3]);
-                acc3 = fma_h<1>(acc3, vw[3], xo[3]);
             }
         }
         // every sub-step that was skipped lies behind the end of all rows of the warp: `run` is not used again before the next row resets it
@@ -423,15 +512,15 @@ bool use_pdl()
     return on;
 }
 
-template <int L, int NPAIR, bool XS, bool PEER = false>
+template <int L, int NPAIR, bool XS, bool PEER = false, int BV = 1>
 int launch(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
            const void *x, void *y, float alpha, float beta, cudaStream_t stream,
-           const DeviceInfo &dev, int ctas_per_sm, const Peers &peers = Peers{})
+           const DeviceInfo &dev, int ctas_per_sm, const Peers &peers = Peers{}, int batch = 1)
 {
-    size_t smem = XS ? (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) : 0;
+    size_t smem = XS ? (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) * BV : 0;
     if (PEER)  // staging area for a CTA's slice of y (a CTA never owns more rows than rows / #SMs + rounding)
         smem = ((smem + 15) & ~(size_t)15) + (size_t)(rows / dev.sm_count + kWarpsPerCta * 8 + 8) * sizeof(__half);
-    auto kernel = spmv_kernel<L, NPAIR, XS, PEER>;
+    auto kernel = spmv_kernel<L, NPAIR, XS, PEER, BV>;
     if (smem > 48 * 1024) {
         // Idempotent and cheap; set on every call so that every device is covered.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -458,7 +547,7 @@ int launch(const void *values, const void *deltas, const int32_t *ri, int rows, 
     cfg.numAttrs = (use_pdl() && !PEER) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel,
         static_cast<const uint4 *>(values), static_cast<const unsigned *>(deltas), ri,
-        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta, peers);
+        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta, peers, batch);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "spmv launch: %s", cudaGetErrorString(e));
     return MACKO_OK;
@@ -489,6 +578,23 @@ int launch_l(int L, int D, const void *values, const void *deltas, const int32_t
         case 32: return launch_d<32, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
         default: return fail(MACKO_ERR_INVALID_ARGUMENT, "lanes_per_row must be 4, 8, 16 or 32 (got %d)", L);
     }
+}
+
+// One launch for up to BV vectors. Lanes per row as in the single-vector product; fewer units in flight with
+// more vectors, whose accumulators and gathered values take the registers.
+template <int BV>
+int launch_batched(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
+                   const void *x, void *y, int batch, float alpha, float beta, cudaStream_t stream, const DeviceInfo &dev)
+{
+    const long long avg_row = padded / rows;
+    const bool wide = rows < 16384;
+    if constexpr (BV <= 4) {
+        if (avg_row > (long long)(wide ? 32 : 8) * kGroup * 2)
+            return wide ? launch<32, 2, true, false, BV>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, 0, Peers{}, batch)
+                        : launch<8, 2, true, false, BV>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, 0, Peers{}, batch);
+    }
+    return wide ? launch<32, 1, true, false, BV>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, 0, Peers{}, batch)
+                : launch<8, 1, true, false, BV>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, 0, Peers{}, batch);
 }
 
 int check_args(const void *values, const void *deltas, const int32_t *ri, int64_t rows, int64_t cols,
@@ -570,6 +676,46 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
     if (xs)
         return launch_l<true>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
     return launch_l<false>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
+}
+
+int macko_spmm_fp16(const void *values, const void *deltas, const int32_t *row_indices,
+                    int64_t rows, int64_t cols, int64_t padded_count,
+                    const void *x, void *y, int64_t batch, float alpha, float beta, void *stream)
+{
+    using namespace macko;
+    if (batch < 0) return fail(MACKO_ERR_INVALID_ARGUMENT, "negative batch %lld", (long long)batch);
+    if (batch == 0) return MACKO_OK;   // nothing to read or write: x and y may be null
+    int st = check_args(values, deltas, row_indices, rows, cols, padded_count, x, y);
+    if (st != MACKO_OK) return st;
+    if (rows == 0) return MACKO_OK;
+    const DeviceInfo *dev = nullptr;
+    st = current_device_info(&dev);
+    if (st != MACKO_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t per_vector = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
+    const char *xp = static_cast<const char *>(x);
+    char *yp = static_cast<char *>(y);
+    // Chunks of up to 8 vectors per pass over the matrix, fewer when that many copies of x do not fit
+    // shared memory; what is left over goes through the single-vector product.
+    int64_t done = 0;
+    while (done < batch) {
+        const int64_t left = batch - done;
+        int bv = left >= 5 ? 8 : left >= 3 ? 4 : left >= 2 ? 2 : 1;
+        while (bv > 1 && per_vector * bv > (size_t)dev->max_smem_optin) bv >>= 1;
+        const int now = (int)(left < bv ? left : bv);
+        const void *xc = xp + (size_t)done * cols * sizeof(__half);
+        void *yc = yp + (size_t)done * rows * sizeof(__half);
+        const int r = (int)rows, c = (int)cols;
+        switch (bv) {
+            case 8: st = launch_batched<8>(values, deltas, row_indices, r, c, padded_count, xc, yc, now, alpha, beta, s, *dev); break;
+            case 4: st = launch_batched<4>(values, deltas, row_indices, r, c, padded_count, xc, yc, now, alpha, beta, s, *dev); break;
+            case 2: st = launch_batched<2>(values, deltas, row_indices, r, c, padded_count, xc, yc, now, alpha, beta, s, *dev); break;
+            default: st = macko_spmv_fp16(values, deltas, row_indices, rows, cols, padded_count, xc, yc, alpha, beta, stream); break;
+        }
+        if (st != MACKO_OK) return st;
+        done += now;
+    }
+    return MACKO_OK;
 }
 
 int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_t *row_indices,

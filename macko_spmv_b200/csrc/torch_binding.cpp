@@ -76,6 +76,37 @@ void multiply_out_cuda(const at::Tensor &values, const at::Tensor &deltas, const
                  "macko_spmv_fp16");
 }
 
+// Y[batch, rows] for V[batch, cols]: up to 8 vectors per pass over the compressed matrix.
+at::Tensor multiply_batched_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
+                                 int64_t rows, int64_t cols, const at::Tensor &V)
+{
+    check_compressed(values, deltas, ri, rows, cols);
+    TORCH_CHECK(V.dtype() == at::kHalf, "V must be torch.half");
+    TORCH_CHECK(V.is_cuda() && V.device() == values.device(), "V must be on the device of M");
+    TORCH_CHECK(V.is_contiguous(), "V must be contiguous");
+    TORCH_CHECK(V.dim() == 2 && V.size(1) == cols, "V must have shape [batch, M_cols]");
+    const c10::cuda::CUDAGuard guard(values.device());
+    at::Tensor y = at::empty({V.size(0), rows}, values.options());
+    cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
+    check_status(macko_spmm_fp16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                 values.numel(), V.data_ptr(), y.data_ptr(), V.size(0), 1.0f, 0.0f, stream),
+                 "macko_spmm_fp16");
+    return y;
+}
+
+at::Tensor decompress_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
+                           int64_t rows, int64_t cols)
+{
+    check_compressed(values, deltas, ri, rows, cols);
+    const c10::cuda::CUDAGuard guard(values.device());
+    at::Tensor dense = at::empty({rows, cols}, values.options());
+    cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
+    check_status(macko_decompress_fp16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                       values.numel(), dense.data_ptr(), stream),
+                 "macko_decompress_fp16");
+    return dense;
+}
+
 std::tuple<at::Tensor, at::Tensor, at::Tensor> compress_cuda(const at::Tensor &M)
 {
     TORCH_CHECK(M.is_cuda(), "M must be a CUDA tensor");
@@ -109,6 +140,8 @@ TORCH_LIBRARY(macko_spmv, m)
     m.def("multiply_out(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor V, "
           "Tensor(a!) y, float alpha, float beta) -> ()");
     m.def("compress_dense(Tensor M) -> (Tensor, Tensor, Tensor)");
+    m.def("multiply_batched(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor V) -> Tensor");
+    m.def("decompress(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
@@ -116,4 +149,6 @@ TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
     m.impl("multiply", &multiply_cuda);
     m.impl("multiply_out", &multiply_out_cuda);
     m.impl("compress_dense", &compress_cuda);
+    m.impl("multiply_batched", &multiply_batched_cuda);
+    m.impl("decompress", &decompress_cuda);
 }

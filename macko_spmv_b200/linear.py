@@ -7,7 +7,9 @@ calls `multiply` once per input vector through `torch.vmap`
 each `<name>.weight` is replaced by `<name>.c_0 … <name>.c_4` = values, deltas, row_indices, rows, cols
 (python_scripts/util_compress_llm.py:16-44). This module keeps that key layout, so checkpoints written
 by either implementation load in the other, and routes batches itself: inputs of shape [..., in]
-are flattened and multiplied vector by vector on the current stream (decode is the batch-1 case).
+are flattened; one vector goes through `multiply` (decode), a few vectors share passes over the
+compressed matrix (`multiply_batched`, 8 per pass), and large batches (prefill) run as a dense GEMM on a
+decompressed copy.
 """
 from __future__ import annotations
 
@@ -56,7 +58,7 @@ class MackoLinear(nn.Module):
         return (self.c_0, self.c_1, self.c_2, self.out_features, self.in_features)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        from . import multiply
+        from . import multiply, multiply_batched
 
         if x.shape[-1] != self.in_features:
             raise RuntimeError(f"expected last dimension {self.in_features}, got {tuple(x.shape)}")
@@ -66,7 +68,7 @@ class MackoLinear(nn.Module):
         if flat.shape[0] == 1:
             y = multiply(comp, flat[0].contiguous()).unsqueeze(0)
         else:
-            y = torch.stack([multiply(comp, flat[i].contiguous()) for i in range(flat.shape[0])])
+            y = multiply_batched(comp, flat.contiguous())
         if self.bias is not None:
             y = y + self.bias
         return y.reshape(*lead, self.out_features)
