@@ -39,7 +39,7 @@ UNIT = "us"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum over the 36 spmv launches of one step, from the
 # ncu capture summarised in profiles/spmv_sweep_launches.md (None until captured).
-NCU_STEP_TRAFFIC_BYTES = 2729379584
+NCU_STEP_TRAFFIC_BYTES = 2728741376
 
 
 def measured_hbm_peak():
@@ -246,6 +246,31 @@ def sharded_large_leg(device, rank, world, lib, peer, peak_gbs, reps=40):
         for c in cases:
             product(c)
     torch.cuda.synchronize()
+    # the four products as one CUDA graph: device time of a cycle without host launch overhead
+    graph_us = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for c in cases:
+                product(c)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1000.0 / reps], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        graph_us = float(t.item())
+    except Exception:   # capture refused: the eager figures below still stand
+        graph_us = None
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(cases) + 1)] for _ in range(reps)]
@@ -269,6 +294,44 @@ def sharded_large_leg(device, rank, world, lib, peer, peak_gbs, reps=40):
             row["cublas_gemv_us"] = round(c["gemv_us"], 2)
             row["speedup_vs_cublas"] = round(c["gemv_us"] / t, 3)
         out.append(row)
+    total_bytes = sum(c["bytes"] for c in cases)
+    return {"cases": out, "us_sum_eager": round(sum(r["us"] for r in out), 2),
+            "us_sum_graph": None if graph_us is None else round(graph_us, 2),
+            "per_gpu_roofline_frac_graph": None if graph_us is None else round(total_bytes / (graph_us * 1e-6) / 1e9 / peak_gbs, 4)}
+
+
+# --------------------------------------------------------------------------- several right-hand sides
+
+def batched_leg(device):
+    """The 11008x4096 layer at density 0.5 with several right-hand sides: one pass over the compressed
+    matrix per 8 vectors (`multiply_batched`) against a loop of single-vector products, and the dense-copy
+    route for a prefill-sized batch. Microseconds per call, same matrix every call (warm L2 where it fits)."""
+    import macko_spmv_b200 as macko_spmv
+    from macko_spmv_b200 import workloads
+
+    rows, cols = 11008, 4096
+    comp = macko_spmv.compress(workloads.magnitude_pruned_matrix(rows, cols, 0.5, 2913, device=device))
+
+    def timed(fn, reps=40):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return round(e0.elapsed_time(e1) * 1000.0 / reps, 2)
+
+    out = {"shape": [rows, cols], "density": 0.5}
+    V = torch.randn(128, cols, device=device).half()
+    out["single_us"] = timed(lambda: macko_spmv.multiply(comp, V[0]))
+    for b in (2, 4, 8, 16):
+        Vb = V[:b].contiguous()
+        out[f"batched_{b}_us"] = timed(lambda: macko_spmv.multiply_batched(comp, Vb))
+    V8 = V[:8].contiguous()
+    out["loop_of_8_us"] = timed(lambda: [macko_spmv.multiply(comp, V8[i]) for i in range(8)])
+    out["prefill_128_dense_route_us"] = timed(lambda: macko_spmv.multiply_batched(comp, V))
     return out
 
 
@@ -503,6 +566,7 @@ def run_own_arm(args):
     large = None
     if not args.no_sharded_large and (world == 1 or peer is not None):
         large = sharded_large_leg(device, rank, world, lib, peer, peak_gbs)
+    batched = batched_leg(device) if (world == 1 and not args.no_batched) else None
     cpu_base = cpu_reference_path(3, 1, gpu_cases=cases) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
 
     if rank == 0:
@@ -544,7 +608,11 @@ def run_own_arm(args):
             line["sharded_large"] = {
                 "workload": "12288x49152 and 49152x12288, Bernoulli mask at densities 0.1 and 0.5, contiguous row block per GPU, "
                             "full y on every rank; microseconds per product, max over ranks, products back to back",
-                "cases": large, "us_sum": round(sum(r["us"] for r in large), 2)}
+                "note": "per-case figures are eager launches between CUDA events (they include host launch gaps when a product is "
+                        "shorter than the host's launch path); us_sum_graph replays the four products as one CUDA graph",
+                **large}
+        if batched is not None:
+            line["batched"] = batched
         if per_case is not None:
             line["per_case"] = per_case
             sp = [p["speedup_vs_cublas"] for p in per_case]
@@ -595,6 +663,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-per-case", action="store_true", help="skip the per-matrix cuBLAS comparison")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-batched", action="store_true", help="skip the multi-vector product figures")
     ap.add_argument("--no-sharded-large", action="store_true", help="skip the large row-sharded matrices")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how the y slices are exchanged (fused peer stores, or NCCL all-gather)")
