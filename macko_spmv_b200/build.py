@@ -2,6 +2,7 @@
 
 ``libmacko_b200.so``  CUDA kernels + C ABI (nvcc, sm_100a only, no torch dependency)
 ``_torch_ops.so``     the `macko_spmv::*` torch operators, linked against the C ABI
+``macko_bench``       command-line benchmark with the reference CLI's arguments (C ABI + cuBLAS)
 
 Run ``python macko_spmv_b200/build.py`` (or call :func:`build`). Nothing is compiled at
 import time; importing the package without the built libraries raises.
@@ -18,6 +19,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_CORE = os.path.join(PKG_DIR, "libmacko_b200.so")
 LIB_TORCH = os.path.join(PKG_DIR, "_torch_ops.so")
+BENCH_CLI = os.path.join(PKG_DIR, "macko_bench")
 
 CUDA_SOURCES = ["common.cu", "spmv.cu", "compress.cu", "decompress.cu"]
 NVCC_FLAGS = [
@@ -99,11 +101,21 @@ def build_torch_ops(force: bool = False, verbose: bool = False) -> str:
     return LIB_TORCH
 
 
+def build_cli(force: bool = False, verbose: bool = False) -> str:
+    src = os.path.join(CSRC, "bench_cli.cu")
+    if not force and _newer(BENCH_CLI, [src, LIB_CORE, os.path.join(INCLUDE, "macko_b200.h"), __file__]):
+        return BENCH_CLI
+    _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-I", INCLUDE, src, "-o", BENCH_CLI,
+          "-L", PKG_DIR, "-l:libmacko_b200.so", "-lcublas", "-Xlinker", "-rpath=$ORIGIN"], verbose)
+    return BENCH_CLI
+
+
 def build(force: bool = False, verbose: bool = False) -> None:
     build_core(force, verbose)
     build_torch_ops(force, verbose)
+    build_cli(force, verbose)
 
 
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv)
-    print("built", LIB_CORE, LIB_TORCH)
+    print("built", LIB_CORE, LIB_TORCH, BENCH_CLI)

@@ -96,6 +96,22 @@ class Block(nn.Module):
         return x + self.down_proj(torch.nn.functional.silu(gu[: self.ffn]) * gu[self.ffn :])
 
 
+    def prefill(self, x, cos, sin):
+        """All prompt positions at once: x [T, hidden], cos/sin [T, head_dim]. Fills cache rows 0..T-1."""
+        T = x.shape[0]
+        qkv = self.qkv_proj(self.input_norm(x)).view(T, 3, self.heads, self.head_dim)
+        qk = _rope(qkv[:, :2], cos[:, None, None, :], sin[:, None, None, :])          # [T, 2, heads, head_dim]
+        q = qk[:, 0].transpose(0, 1).unsqueeze(0)                                      # [1, heads, T, head_dim]
+        k = qk[:, 1].transpose(0, 1).unsqueeze(0)
+        v = qkv[:, 2].transpose(0, 1).unsqueeze(0)
+        self.k_cache[:, :, :T] = k
+        self.v_cache[:, :, :T] = v
+        attn = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.o_proj(attn[0].transpose(0, 1).reshape(T, self.hidden))
+        gu = self.gate_up_proj(self.post_norm(x))
+        return x + self.down_proj(torch.nn.functional.silu(gu[:, : self.ffn]) * gu[:, self.ffn :])
+
+
 def _rope(t, cos, sin):
     # rotate-half convention: (t1, t2) -> (t1*cos - t2*sin, t2*cos + t1*sin), cos/sin repeated over both halves
     half = t.shape[-1] // 2
@@ -131,6 +147,17 @@ class LlamaDecoder(nn.Module):
         """token int64[1], pos int64[1] (device tensors) -> next token int64[1] (greedy)."""
         return torch.argmax(self.logits(token, pos).float(), dim=-1, keepdim=True)
 
+    def prefill(self, tokens):
+        """Runs the whole prompt (int64 [T]) in one pass (the linear layers see a [T, hidden] batch and route
+        it through the multi-vector product or the dense-copy GEMM); returns the greedy next token [1]."""
+        T = tokens.numel()
+        x = self.embed.index_select(0, tokens)
+        cos, sin = self.cos_table[:T], self.sin_table[:T]
+        for blk in self.blocks:
+            x = blk.prefill(x, cos, sin)
+        logits = self.lm_head(self.norm(x[T - 1]))
+        return torch.argmax(logits.float(), dim=-1, keepdim=True)
+
     def logits(self, token, pos):
         """fp16 logits [vocab] of the token at position `pos`; updates the KV cache."""
         x = self.embed.index_select(0, token)[0]
@@ -143,9 +170,10 @@ class LlamaDecoder(nn.Module):
 
 
 @torch.no_grad()
-def generate(model: LlamaDecoder, prompt: torch.Tensor, new_tokens: int, use_graph: bool = True):
-    """Feeds the prompt token by token, then generates greedily. Returns (tokens, seconds for the
-    generated part, seconds for the prompt part)."""
+def generate(model: LlamaDecoder, prompt: torch.Tensor, new_tokens: int, use_graph: bool = True,
+             batched_prefill: bool = False):
+    """Feeds the prompt (token by token through the decode step, or in one batched pass), then generates
+    greedily. Returns (tokens, seconds for the generated part, seconds for the prompt part)."""
     dev = model.device
     token = torch.zeros(1, dtype=torch.int64, device=dev)
     pos = torch.zeros(1, dtype=torch.int64, device=dev)
@@ -172,10 +200,13 @@ def generate(model: LlamaDecoder, prompt: torch.Tensor, new_tokens: int, use_gra
     tokens = []
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for i in range(prompt.numel()):
-        token.copy_(prompt[i : i + 1])
-        pos.fill_(i)
-        run_step()
+    if batched_prefill:
+        out_token.copy_(model.prefill(prompt))
+    else:
+        for i in range(prompt.numel()):
+            token.copy_(prompt[i : i + 1])
+            pos.fill_(i)
+            run_step()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     for i in range(new_tokens):
@@ -196,6 +227,8 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--dense-lm-head", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--batched-prefill", action="store_true",
+                    help="run the prompt in one pass (one GPU only): linear layers take the [tokens, hidden] batch")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -222,7 +255,10 @@ def main():
     prompt = torch.randint(0, model.cfg["vocab"], (args.prompt,), generator=g, device=device)
     if world > 1:
         dist.barrier()
-    tokens, gen_s, prompt_s = generate(model, prompt, args.new_tokens, use_graph=not args.no_graph)
+    if args.batched_prefill and world > 1:
+        raise SystemExit("--batched-prefill runs on one GPU: the row-sharded layers multiply one vector at a time")
+    tokens, gen_s, prompt_s = generate(model, prompt, args.new_tokens, use_graph=not args.no_graph,
+                                       batched_prefill=args.batched_prefill)
     same = True
     if world > 1:
         t = torch.tensor([gen_s, prompt_s], device=device, dtype=torch.float64)
@@ -241,7 +277,7 @@ def main():
             "prompt_tokens": args.prompt, "new_tokens": args.new_tokens,
             "tokens_per_s": args.new_tokens / gen_s, "prompt_tokens_per_s": args.prompt / prompt_s,
             "build_seconds": build_s, "memory_GB": torch.cuda.max_memory_allocated() / 1e9,
-            "cuda_graph": not args.no_graph, "first_tokens": tokens[:8].tolist(),
+            "cuda_graph": not args.no_graph, "batched_prefill": bool(args.batched_prefill), "first_tokens": tokens[:8].tolist(),
         }), flush=True)
     if world > 1:
         # leave without tearing the communicator down while a captured graph still references it
