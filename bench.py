@@ -229,13 +229,13 @@ def sharded_large_leg(device, rank, world, lib, peer, peak_gbs, reps=40):
                           "bytes": workloads.algorithmic_bytes(comp[0].numel(), hi - lo, cols)})
             del block
     torch.cuda.empty_cache()
-    stream = torch.cuda.current_stream().cuda_stream
 
     def product(c):
         sh = c["shard"]
         if peer is not None:
             return peer.multiply(sh, c["x"])
         comp = sh.compressed
+        stream = torch.cuda.current_stream().cuda_stream   # read at call time: differs under graph capture
         cabi.check(lib, lib.macko_spmv_fp16(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4],
                                             comp[0].numel(), c["x"].data_ptr(), c["y"].data_ptr(), 1.0, 0.0, stream))
         if world > 1:
@@ -526,27 +526,12 @@ def run_own_arm(args):
     # ---- end to end through the public API with host buffers ------------------------------------
     xs_host = [c["x"].cpu().pin_memory() for c in cases]
     ys_host = [torch.empty(c["rows"], dtype=torch.float16).pin_memory() for c in cases]
-    # One GPU: the 36 products are independent, so the (copy in, multiply, copy out) chains are spread over a
-    # few streams and the copies of one chain run under the kernels of the others. Row-sharded runs keep one
-    # stream: the exchange buffers are handed out in launch order.
-    e2e_streams = [torch.cuda.Stream(device=device) for _ in range(4)] if world == 1 else []
-
     def step_e2e():
-        if e2e_streams:
-            main = torch.cuda.current_stream()
-            for st in e2e_streams:
-                st.wait_stream(main)
-            for i, (c, xh, yh) in enumerate(zip(cases, xs_host, ys_host)):
-                with torch.cuda.stream(e2e_streams[i % len(e2e_streams)]):
-                    xd = xh.to(device, non_blocking=True)
-                    y = macko_spmv.multiply(c["comp"], xd)
-                    yh.copy_(y, non_blocking=True)
-            for st in e2e_streams:
-                main.wait_stream(st)
-            return
         for c, sh, xh, yh in zip(cases, shards, xs_host, ys_host):
             xd = xh.to(device, non_blocking=True)
-            if peer is not None:
+            if world == 1:
+                y = macko_spmv.multiply(c["comp"], xd)
+            elif peer is not None:
                 y = peer.multiply(sh, xd)
             else:
                 y = sharded.multiply_sharded(sh, xd)
@@ -607,8 +592,7 @@ def run_own_arm(args):
                 "value": e2e_ms * 1000.0, "unit": UNIT,
                 "h2d_bytes_per_step": sum(2 * c["cols"] for c in cases),
                 "d2h_bytes_per_step": sum(2 * c["rows"] for c in cases),
-                "api": "macko_spmv_b200.multiply(compressed, x) per matrix; x from pinned host memory, y copied to pinned host memory; compressed matrix resident on the device as the API requires"
-                       + ("; the 36 independent chains are issued round-robin on 4 CUDA streams" if world == 1 else ""),
+                "api": "macko_spmv_b200.multiply(compressed, x) per matrix; x from pinned host memory, y copied to pinned host memory; compressed matrix resident on the device as the API requires",
             },
             "gpu_launches": args.steps * n_cases,
             "clocks": clocks,

@@ -12,12 +12,9 @@ namespace macko {
 namespace {
 
 constexpr int kWarps = 8;        // warps (rows in flight) per CTA
-constexpr int kCtasPerSm = 5;    // 40 resident warps per SM: the kernel lives on loads in flight
-// A step decodes 256 stored elements. The columns it covers (from the end of the previous step; at most
-// 15 + 256 * 16, since consecutive stored elements are at most 16 columns apart) are emitted in windows of
-// kWindow columns through a small per-warp buffer: dense rows need one window per step, sparse ones a few.
-constexpr int kWindow = 1024;
-constexpr int kStage = kWindow + 8;   // fp16 slots of a warp's staging buffer: a window plus alignment slack
+// A step decodes 256 stored elements; consecutive stored elements are at most 16 columns apart, so the
+// columns a step covers (from the end of the previous step) fit 15 + 256 * 16 slots; 7 more for alignment.
+constexpr int kStage = 4128;     // fp16 slots of a warp's staging buffer (a multiple of 8)
 
 // dense[g0 .. g0 + n) = stage[off .. off + n) with 16-byte stores wherever source and destination allow.
 // `stage` index 0 corresponds to global index g0 - off, which is a multiple of 8, so aligned 8-element
@@ -40,7 +37,7 @@ __device__ __forceinline__ void flush_span(unsigned short *__restrict__ dense, l
 // One warp per row. Each step's columns are assembled in the warp's shared-memory buffer (zeros, then the
 // stored elements scattered to their columns) and written out with coalesced 16-byte stores, so the dense
 // matrix is written exactly once and no separate clearing pass is needed.
-__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
+__global__ void __launch_bounds__(kWarps * 32)
 decompress_rows_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
                        const int *__restrict__ ri, int rows, int cols, int stored,
                        unsigned short *__restrict__ dense, bool vec_ok)
@@ -65,15 +62,14 @@ decompress_rows_kernel(const uint4 *__restrict__ values, const unsigned *__restr
                 w = __ldg(deltas + (first >> 3));
             }
             const unsigned short *vh = reinterpret_cast<const unsigned short *>(&v);
-            // columns relative to the lane's start (inclusive delta prefix + index, at most 127), one per byte;
-            // 0xff marks elements outside the row
-            unsigned rel[2] = {0u, 0u};
+            // columns relative to the lane's start: inclusive delta prefix + index, for elements inside the row
+            int rel[8];
             int sum = 0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const bool inside = first + j >= begin && first + j < end;
                 if (inside) sum += (int)((w >> (4 * j)) & 15u) + 1;
-                rel[j >> 2] |= (inside ? (unsigned)(sum - 1) : 0xffu) << (8 * (j & 3));
+                rel[j] = inside ? sum - 1 : -1;
             }
             int inc = sum;
 #pragma unroll
@@ -85,24 +81,21 @@ decompress_rows_kernel(const uint4 *__restrict__ values, const unsigned *__restr
             col_base += __shfl_sync(0xffffffffu, inc, 31);
             // this step delivers columns [written, step_end): the gap since the last step, then its elements
             const int step_end = min(col_base, cols);
-            for (int wbase = written; wbase < step_end; wbase += kWindow) {
-                const int n = min(kWindow, step_end - wbase);
-                const long long g0 = row0 + wbase;
-                const int off = (int)(g0 & 7);
-                uint4 *z = reinterpret_cast<uint4 *>(stage);
-                for (int c = lane; c < (off + n + 7) >> 3; c += 32) z[c] = make_uint4(0u, 0u, 0u, 0u);
-                __syncwarp();
+            const int n = step_end - written;
+            if (n <= 0 || n > kStage - 8) continue;   // nothing new, or deltas that no compressor can produce
+            const long long g0 = row0 + written;
+            const int off = (int)(g0 & 7);
+            uint4 *z = reinterpret_cast<uint4 *>(stage);
+            for (int c = lane; c < (off + n + 7) >> 3; c += 32) z[c] = make_uint4(0u, 0u, 0u, 0u);
+            __syncwarp();
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const unsigned r = (rel[j >> 2] >> (8 * (j & 3))) & 0xffu;
-                    const int col = lane_base + (int)r - wbase;   // column inside the window
-                    if (r != 0xffu && col >= 0 && col < n && (vh[j] & 0x7fffu) != 0u) stage[off + col] = vh[j];
-                }
-                __syncwarp();
-                flush_span(dense, g0, n, stage, off, vec_ok, lane);
-                __syncwarp();
+            for (int j = 0; j < 8; ++j) {
+                const int col = lane_base + rel[j];
+                if (rel[j] >= 0 && col >= written && col < step_end && (vh[j] & 0x7fffu) != 0u) stage[off + col - written] = vh[j];
             }
-            if (step_end <= written) continue;   // nothing new (only possible with malformed input)
+            __syncwarp();
+            flush_span(dense, g0, n, stage, off, vec_ok, lane);
+            __syncwarp();
             written = step_end;
         }
         flush_span(dense, row0 + written, cols - written, nullptr, (int)((row0 + written) & 7), vec_ok, lane);   // zeros behind the last stored element
@@ -135,7 +128,7 @@ extern "C" int macko_decompress_fp16(const void *values, const void *deltas, con
     cudaError_t e = cudaFuncSetAttribute(decompress_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     long long grid = (rows + kWarps - 1) / kWarps;
-    const long long cap = (long long)dev->sm_count * kCtasPerSm;
+    const long long cap = (long long)dev->sm_count * 3;   // three CTAs per SM fit by shared memory
     if (grid > cap) grid = cap;
     decompress_rows_kernel<<<(unsigned)grid, kWarps * 32, smem, s>>>(
         static_cast<const uint4 *>(values), static_cast<const unsigned *>(deltas), row_indices, (int)rows, (int)cols,

@@ -580,6 +580,31 @@ int launch_l(int L, int D, const void *values, const void *deltas, const int32_t
     }
 }
 
+// Lanes per row (L) and units in flight per lane (D) for a matrix, calibrated on B200 over row counts
+// 4096..49152, row lengths 500..25000 stored elements and densities 0.1..0.9:
+//   * fewer lanes per row keep the x gathers of one load instruction close together (fewer shared-memory bank
+//     conflicts, the resource the kernel is bound by) and shorten the cross-lane scan, so the smallest L wins
+//     that still (a) gives at least ~0.55 of the resident warps a block of rows and (b) walks a row in at most
+//     ~64 sub-steps (a row is a serial chain of sub-steps; 16 sub-steps for very wide matrices, where a full
+//     warp per row measured better);
+//   * rows shorter than half a sub-step shrink the group further;
+//   * six units in flight once a row holds more than three sub-steps, four above one, else two.
+struct Shape { int L, D; };
+Shape choose_shape(long long rows, long long cols, long long padded, int resident_warps)
+{
+    const long long avg_row = rows > 0 ? padded / rows : 0;
+    const long long chain = cols > 16384 ? 16 : 64;
+    int L = 32;
+    for (int cand = 8; cand < 32; cand <<= 1) {
+        const bool enough_blocks = rows * cand * 100 >= 55LL * 32 * resident_warps;
+        const bool short_chain = avg_row <= chain * kGroup * cand;
+        if (enough_blocks && short_chain) { L = cand; break; }
+    }
+    while (L > 4 && avg_row < (long long)L * kGroup / 2) L >>= 1;
+    const int D = avg_row > 3LL * L * kGroup ? 6 : avg_row > (long long)L * kGroup ? 4 : 2;
+    return {L, D};
+}
+
 // One launch for up to BV vectors. Lanes per row as in the single-vector product; fewer units in flight with
 // more vectors, whose accumulators and gathered values take the registers.
 template <int BV>
@@ -660,17 +685,10 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
     st = current_device_info(&dev);
     if (st != MACKO_OK) return st;
 
-    // Shape heuristics, calibrated on B200 over row counts 4096..49152 and densities 0.1..0.9.
-    // A full warp per row gives the finest balance across warps and wins while a matrix has fewer
-    // rows than a few per resident warp; with many rows, 8 lanes per row keep the x gathers of one
-    // instruction close together (fewer shared-memory bank conflicts) and shorten the cross-lane
-    // scan. Short rows shrink the group so that a row fills at least half of one sub-step.
-    const long long avg_row = padded_count / rows;
-    int L = rows >= 16384 ? 8 : 32;
-    while (L > 4 && avg_row < (long long)L * kGroup / 2) L >>= 1;
-    int D = avg_row > (long long)L * kGroup * 2 ? 4 : 2;
-    if (L == 8 && avg_row > (long long)L * kGroup * 6) D = 6;   // measured: 5-9 % faster than 4 with 8 lanes per row
     const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
+    const int ctas = smem * 2 + 2048 <= (size_t)dev->max_smem_optin ? 2 : 1;
+    const Shape shape = choose_shape(rows, cols, padded_count, dev->sm_count * ctas * kWarpsPerCta);
+    const int L = shape.L, D = shape.D;
     const bool xs = smem <= (size_t)dev->max_smem_optin;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (xs)
@@ -749,15 +767,24 @@ int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_
         return fail(MACKO_ERR_INVALID_ARGUMENT, "cols=%lld does not fit shared memory in the scatter variant", (long long)cols);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // rows == 0 still has to signal: launch the kernel with an empty range (one CTA)
-    const long long avg_row = rows > 0 ? padded_count / rows : 0;
-    const bool wide = rows < 16384;
-    const bool deep = avg_row > (long long)(wide ? 32 : 8) * kGroup * 2;
+    const int ctas = smem * 2 + 4096 <= (size_t)dev->max_smem_optin ? 2 : 1;
+    Shape shape = choose_shape(rows, cols, padded_count, dev->sm_count * ctas * kWarpsPerCta);
+    if (shape.L < 8) shape.L = 8;   // the scatter variant is built for 8, 16 and 32 lanes per row
     const int r = (int)rows, c = (int)cols;
-    if (wide)
-        return deep ? launch<32, 2, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers)
-                    : launch<32, 1, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers);
-    return deep ? launch<8, 2, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers)
-                : launch<8, 1, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers);
+#define MACKO_SCATTER(LL, NP) \
+    launch<LL, NP, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers)
+    switch (shape.L * 10 + shape.D) {
+        case 82: return MACKO_SCATTER(8, 1);
+        case 84: return MACKO_SCATTER(8, 2);
+        case 86: return MACKO_SCATTER(8, 3);
+        case 162: return MACKO_SCATTER(16, 1);
+        case 164: return MACKO_SCATTER(16, 2);
+        case 166: return MACKO_SCATTER(16, 3);
+        case 322: return MACKO_SCATTER(32, 1);
+        case 324: return MACKO_SCATTER(32, 2);
+        default: return MACKO_SCATTER(32, 3);
+    }
+#undef MACKO_SCATTER
 }
 
 int macko_peer_wait(uint32_t *local_flags, int world, void *stream)

@@ -197,6 +197,8 @@ def generate(model: LlamaDecoder, prompt: torch.Tensor, new_tokens: int, use_gra
         else:
             out_token.copy_(model.step(token, pos))
 
+    if batched_prefill:
+        model.prefill(prompt)   # untimed first pass, like the warm-up runs of the decode step: allocator growth, GEMM set-up
     tokens = []
     torch.cuda.synchronize()
     t0 = time.perf_counter()
