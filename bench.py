@@ -39,7 +39,7 @@ UNIT = "us"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum over the 36 spmv launches of one step, from the
 # ncu capture summarised in profiles/spmv_sweep_launches.md (None until captured).
-NCU_STEP_TRAFFIC_BYTES = 2728741376
+NCU_STEP_TRAFFIC_BYTES = 2730896128
 
 
 def measured_hbm_peak():
