@@ -310,6 +310,46 @@ def test_skewed_rows():
     _check_y(macko_spmv.multiply(comp, x), comp_np, _u16(x), "skewed")
 
 
+@pytest.mark.parametrize("shape", [(3000, 8192), (700, 28672), (40, 4096)])
+def test_long_rows_among_short_ones_every_kernel_shape(shape):
+    """Rows far longer than the average next to short and empty ones: dense rows, rows that start and end
+    inside an 8-element unit, medium rows, for every lanes-per-row / units-in-flight combination through the
+    default entry point and the tuned one; a second run must give the same bits."""
+    rows, cols = shape
+    lib = cabi.load()
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    M = workloads.bernoulli_matrix(rows, cols, 0.03, seed=rows + 1, device="cuda")
+    dense_rows = torch.randperm(rows, generator=g, device="cuda")[: max(2, rows // 12)]
+    M[dense_rows] = (torch.randn(dense_rows.numel(), cols, generator=g, device="cuda") * 0.5).half()
+    M[dense_rows[0], :3] = 0          # a long row that starts late ...
+    M[dense_rows[1], cols - 5 :] = 0   # ... and one that ends early
+    half_rows = torch.randperm(rows, generator=g, device="cuda")[: max(1, rows // 20)]
+    M[half_rows, : cols // 2] = 1.0    # medium rows: longer than twice the average, shorter than dense
+    M[1] = 0
+    comp = macko_spmv.compress(M)
+    comp_np = oracle.compress(_u16(M).reshape(rows, cols))
+    _assert_buffers_equal(comp, comp_np, "long rows")
+    x = workloads.dense_vector(cols, 9, "cuda")
+    xn = _u16(x)
+    _check_y(macko_spmv.multiply(comp, x), comp_np, xn, "default entry")
+    stream = torch.cuda.current_stream().cuda_stream
+    for L in (4, 8, 16, 32):
+        for D in (2, 4, 6):
+            y = torch.full((rows,), float("nan"), dtype=torch.float16, device="cuda")
+            cabi.check(lib, lib.macko_spmv_fp16_tuned(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), rows, cols,
+                                                      comp[0].numel(), x.data_ptr(), y.data_ptr(), 1.0, 0.0, stream, L, D, 1, 0))
+            _check_y(y, comp_np, xn, f"L={L} D={D}")
+            again = torch.empty_like(y)
+            cabi.check(lib, lib.macko_spmv_fp16_tuned(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), rows, cols,
+                                                      comp[0].numel(), x.data_ptr(), again.data_ptr(), 1.0, 0.0, stream, L, D, 1, 0))
+            assert torch.equal(y.view(torch.int16), again.view(torch.int16)), "rows must sum in a fixed order"
+    # alpha / beta on long rows
+    y0 = torch.ones(rows, dtype=torch.float16, device="cuda")
+    torch.ops.macko_spmv.multiply_out(comp[0], comp[1], comp[2], rows, cols, x, y0, 0.5, 2.0)
+    ref = macko_spmv.multiply(comp, x).float() * 0.5 + 2.0
+    assert torch.allclose(y0.float(), ref, rtol=2e-3, atol=2e-3 * float(ref.abs().max()))
+
+
 def test_corrupt_row_indices_stay_in_bounds():
     # Offsets outside [0, P] are clamped inside the kernel: rows that use them give garbage, but no
     # load leaves the buffers and rows with intact offsets keep their exact result.
