@@ -81,6 +81,15 @@ int macko_spmv_fp16_tuned(const void *values, const void *deltas, const int32_t 
                           int lanes_per_row, int steps_in_flight, int x_in_shared, int ctas_per_sm);
 
 /*
+ * The launch shape macko_spmv_fp16 picks for a matrix on a GPU with `sm_count` SMs: lanes per row (4, 8, 16
+ * or 32) and 8-element units in flight per lane (2, 4 or 6), the two arguments macko_spmv_fp16_tuned takes.
+ * Pure host arithmetic (no CUDA call), for logging and for tests of the heuristic. No counterpart in the
+ * reference, whose launch shape is fixed (32 x 32 threads, one warp per row, kernels_torch_launchers.cuh:15-16).
+ */
+int macko_spmv_shape(int64_t rows, int64_t cols, int64_t padded_count, int sm_count,
+                     int *lanes_per_row, int *steps_in_flight);
+
+/*
  * Y = alpha * M X + beta * Y for `batch` right-hand sides at once: x is [batch][cols] and y is
  * [batch][rows], both row-major fp16 (the layout of a [tokens, features] activation). Up to 8 vectors
  * share one pass over the compressed matrix (their values are interleaved in shared memory so that one

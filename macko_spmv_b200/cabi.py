@@ -30,6 +30,7 @@ SIGNATURES = {
     "macko_last_error": (ctypes.c_char_p, []),
     "macko_spmv_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp]),
     "macko_spmv_fp16_tuned": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp, _int, _int, _int, _int]),
+    "macko_spmv_shape": (_int, [_i64, _i64, _i64, _int, _vp, _vp]),
     "macko_spmm_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _f, _f, _vp]),
     "macko_decompress_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "macko_compress_count": (_int, [_vp, _i64, _i64, _vp, _vp]),

@@ -10,7 +10,7 @@
 //     picks its next row from the warp's range as soon as it runs out of work, so rows of
 //     different length inside a warp do not wait for each other;
 //   * one unit of a lane = 8 stored elements: one 128-bit load of values and one 32-bit load
-//     of 8 deltas, both straight into registers; 2 or 4 units per lane are issued before any
+//     of 8 deltas, both straight into registers; 2, 4 or 6 units per lane are issued before any
 //     is consumed, and the phases of the computation run over all of them (loads, prefix sums,
 //     scans, gathers) so that independent work hides shuffle and shared-memory latency;
 //   * the 8 column offsets of a unit are produced with byte-SIMD integer arithmetic
@@ -22,7 +22,7 @@
 //     zero-framed copy (masked-out elements read 0 without range checks), and the sm_100
 //     fp16 x fp16 + fp32 fused multiply-add needs no conversions;
 //   * row boundaries that fall inside a unit are handled by masking that unit, only in warps
-//     that actually contain such a unit.
+//     that actually contain such a unit (one warp-wide reduction per iteration finds them).
 #include "common.cuh"
 
 #include <cuda_fp16.h>
@@ -694,6 +694,20 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
     if (xs)
         return launch_l<true>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
     return launch_l<false>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
+}
+
+int macko_spmv_shape(int64_t rows, int64_t cols, int64_t padded_count, int sm_count,
+                     int *lanes_per_row, int *steps_in_flight)
+{
+    using namespace macko;
+    if (rows < 0 || cols < 0 || padded_count < 0 || sm_count <= 0 || !lanes_per_row || !steps_in_flight)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "bad argument to macko_spmv_shape");
+    const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
+    const int ctas = smem * 2 + 2048 <= (size_t)227 * 1024 ? 2 : 1;
+    const Shape shape = choose_shape(rows, cols, padded_count, sm_count * ctas * kWarpsPerCta);
+    *lanes_per_row = shape.L;
+    *steps_in_flight = shape.D;
+    return MACKO_OK;
 }
 
 int macko_spmm_fp16(const void *values, const void *deltas, const int32_t *row_indices,

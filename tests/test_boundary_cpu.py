@@ -96,3 +96,33 @@ def test_fake_tensor_tracing():
         x = torch.empty(40, dtype=torch.float16, device="cuda")
         y = torch.ops.macko_spmv.multiply.default(v, d, ri, 10, 40, x)
         assert y.shape == (10,) and y.dtype == torch.float16 and y.device.type == "cuda"
+
+
+def test_launch_shape_heuristic_table():
+    """The launch shape chosen per matrix (host arithmetic only): the decisions that were calibrated on B200
+    (148 SMs) for the benchmark shapes, and the limits of the rule."""
+    import ctypes
+
+    from macko_spmv_b200 import cabi
+
+    lib = cabi.load()
+
+    def shape(rows, cols, density, pad=1.03):
+        L, D = ctypes.c_int(0), ctypes.c_int(0)
+        P = int(rows * cols * density * pad) // 8 * 8
+        assert lib.macko_spmv_shape(rows, cols, P, 148, ctypes.byref(L), ctypes.byref(D)) == cabi.OK
+        return L.value, D.value
+
+    assert shape(4096, 4096, 0.5) == (32, 6)        # few rows: a warp per row
+    assert shape(4096, 4096, 0.1) == (32, 4)
+    assert shape(4096, 11008, 0.5) == (32, 6)
+    assert shape(8192, 8192, 0.5) == (16, 6)
+    assert shape(11008, 4096, 0.5) == (8, 6)        # enough rows to fill the GPU with 8 lanes per row
+    assert shape(32000, 4096, 0.9) == (8, 6)
+    assert shape(12288, 49152, 0.5) == (32, 6)      # very long rows of a very wide matrix: back to a warp per row
+    assert shape(49152, 12288, 0.5) == (16, 6)
+    assert shape(100000, 64, 0.3)[0] == 4           # rows of ~20 stored elements: the smallest group
+    assert shape(0, 64, 0.5, pad=0) == (4, 2)
+    L, D = ctypes.c_int(0), ctypes.c_int(0)
+    assert lib.macko_spmv_shape(-1, 1, 0, 148, ctypes.byref(L), ctypes.byref(D)) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_spmv_shape(1, 1, 0, 0, ctypes.byref(L), ctypes.byref(D)) == cabi.ERR_INVALID_ARGUMENT
