@@ -441,34 +441,56 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     }
 
     if (PEER) {
-        // The CTA's rows are contiguous: copy its staged slice of y to every rank with coalesced stores
-        // (single 2-byte stores per row would flood NVLink with tiny packets).
+        // Every CTA writes the y values of its (contiguous) rows into this rank's own copy of the full y with
+        // coalesced stores, makes them visible on this GPU and takes a ticket. The CTA that takes the last
+        // ticket then forwards the rank's whole slice to the other ranks over NVLink and publishes it with one
+        // system-scope fence: a system-scope fence in each of the CTAs costs 6-7 us per launch even on one GPU.
         __syncthreads();
         const int n_mine = cta_row_hi - cta_row_lo;
-        for (int p = 0; p < peers.world; ++p) {
-            __half *dst = peers.y[p] + peers.row_offset + cta_row_lo;
+        {
+            __half *dst = peers.y[peers.rank] + peers.row_offset + cta_row_lo;
             for (int i = tid; i < n_mine; i += kThreads) dst[i] = ystage[i];
         }
-        // After the CTA barrier one thread publishes the CTA's peer stores system-wide (the fence is
-        // cumulative over what the barrier ordered before it); the last CTA of the grid then advances
-        // this rank's call counter and releases it into every rank's arrival slot for this rank.
         __shared__ unsigned last_cta_seq;
+        __shared__ unsigned is_last_cta;
         __syncthreads();
         if (tid == 0) {
-            __threadfence_system();
-            unsigned *mine = peers.flags[peers.rank];
-            const unsigned ticket = atomicAdd(mine + peers.world + 1, 1u);
-            unsigned seq = 0u;
-            if (ticket == gridDim.x - 1) {
-                seq = mine[peers.world] + 1u;
+            __threadfence();   // the CTA's stores (ordered before this by the barrier) are visible device-wide before its ticket
+            const unsigned ticket = atomicAdd(peers.flags[peers.rank] + peers.world + 1, 1u);
+            is_last_cta = ticket == gridDim.x - 1;
+            if (is_last_cta) __threadfence();   // ... and the last CTA sees the stores of every CTA whose ticket it has seen
+            last_cta_seq = 0u;
+        }
+        __syncthreads();
+        if (is_last_cta) {
+            // forward this rank's slice (read around L1: other SMs wrote it) to every other rank
+            const unsigned short *src = reinterpret_cast<const unsigned short *>(peers.y[peers.rank] + peers.row_offset);
+            const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+            for (int p = 0; p < peers.world; ++p) {
+                if (p == peers.rank) continue;
+                unsigned short *dst = reinterpret_cast<unsigned short *>(peers.y[p] + peers.row_offset);
+                if (vec && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    const int chunks = rows >> 3;
+                    for (int c = tid; c < chunks; c += kThreads)
+                        reinterpret_cast<uint4 *>(dst)[c] = __ldcg(reinterpret_cast<const uint4 *>(src) + c);
+                    for (int i = (chunks << 3) + tid; i < rows; i += kThreads) dst[i] = __ldcg(src + i);
+                } else {
+                    for (int i = tid; i < rows; i += kThreads) dst[i] = __ldcg(src + i);
+                }
+            }
+            __syncthreads();   // inside a CTA-uniform branch: all forwarding stores are issued
+            if (tid == 0) {
+                __threadfence_system();   // cumulative over what the barrier ordered before it: the forwarded slice is out
+                unsigned *mine = peers.flags[peers.rank];
+                const unsigned seq = mine[peers.world] + 1u;
                 mine[peers.world] = seq;
                 mine[peers.world + 1] = 0u;
                 for (int p = 0; p < peers.world; ++p)   // release at system scope: ordered after everything above
                     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + peers.rank), "r"(seq) : "memory");
+                last_cta_seq = seq;
             }
-            last_cta_seq = seq;
+            __syncthreads();
         }
-        __syncthreads();
         // The CTA that finished last stays until the slices of all other ranks have arrived, so the end of
         // this kernel means that this rank's full y is complete. Its own flags are already out, so no rank
         // waits for a kernel that waits for it; the wait is bounded and records who was missing.
