@@ -178,10 +178,11 @@ int64_t macko_compress_static_capacity(void);
 /*
  * Row-sharded product with the exchange fused into the kernel (several GPUs, one process each).
  * Rank `rank` of `world` (<= 8) holds the compressed block of rows [row_offset, row_offset + rows)
- * and the whole x. Instead of writing a local slice and calling a collective, the kernel stores
- * every y value it produces into the full-y buffer of EVERY rank (`peer_y[p]`, device pointers
- * that are valid on this device: peer-mapped / symmetric memory), and when its grid has finished it
- * advances this rank's call counter and releases it into slot `rank` of every rank's flag array.
+ * and the whole x. Instead of writing a local slice and calling a collective, the kernel delivers
+ * its rows of y into the full-y buffer of EVERY rank (`peer_y[p]`, device pointers that are valid on
+ * this device: peer-mapped / symmetric memory): its CTAs write into `peer_y[rank]`, and the CTA that
+ * finishes last copies the rank's slice from there into the buffers of the other ranks, advances this
+ * rank's call counter and releases it into slot `rank` of every rank's flag array.
  * `peer_flags[p]` points to at least world + 3 zero-initialised uint32 of rank p:
  *   [0, world) arrival counters, [world] calls issued, [world+1] internal ticket, [world+2] error.
  * `peer_y` and `peer_flags` are HOST arrays of `world` pointers, read during the call.
