@@ -633,10 +633,14 @@ template <int BV>
 int launch_batched(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
                    const void *x, void *y, int batch, float alpha, float beta, cudaStream_t stream, const DeviceInfo &dev)
 {
-    const long long avg_row = padded / rows;
-    const bool wide = rows < 16384;
+    // lanes per row as for one vector (the kernel is built for 8 and 32 here), with the resident warps that
+    // BV copies of x in shared memory leave
+    const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) * BV;
+    const int ctas = smem * 2 + 2048 <= (size_t)dev.max_smem_optin ? 2 : 1;
+    const Shape shape = choose_shape(rows, cols, padded, dev.sm_count * ctas * kWarpsPerCta);
+    const bool wide = shape.L >= 16;   // 16 lanes per row are not built for several vectors: a warp per row is the closer choice
     if constexpr (BV <= 4) {
-        if (avg_row > (long long)(wide ? 32 : 8) * kGroup * 2)
+        if (shape.D >= 4)
             return wide ? launch<32, 2, true, false, BV>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, 0, Peers{}, batch)
                         : launch<8, 2, true, false, BV>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, 0, Peers{}, batch);
     }
