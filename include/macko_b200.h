@@ -29,7 +29,17 @@
 extern "C" {
 #endif
 
-#define MACKO_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+#define MACKO_B200_VERSION 200 /* major*10000 + minor*100 + patch */
+
+/* Flag bits of the *_ex / planned / scatter_ex entry points. */
+/* The caller guarantees that values, deltas and row_indices (and the plan, if any) are not written by
+ * work still in flight on `stream` when the call is made: weights compressed at set-up, not the output of
+ * the kernel in front. The kernel may then fetch its first matrix data while the previous kernel of the
+ * stream is still finishing (programmatic dependent launch); x and y are never touched early. */
+#define MACKO_SPMV_MATRIX_IMMUTABLE 1u
+/* macko_spmv_fp16_scatter_ex only: publish this rank's slice and return without waiting for the other
+ * ranks; the caller enqueues macko_peer_wait before the full y is read. */
+#define MACKO_SCATTER_DEFERRED_WAIT 2u
 
 enum macko_status {
     MACKO_OK = 0,
@@ -69,6 +79,26 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
                     const void *x, void *y, float alpha, float beta, void *stream);
 
 /*
+ * macko_spmv_fp16 with flag bits (MACKO_SPMV_MATRIX_IMMUTABLE). Same kernel, same result bits; the flag
+ * only moves the first matrix loads in front of the wait for the previous kernel of the stream.
+ * Replaces the same reference launcher (kernels_torch_launchers.cuh:3-48), which has no such option.
+ */
+int macko_spmv_fp16_ex(const void *values, const void *deltas, const int32_t *row_indices,
+                       int64_t rows, int64_t cols, int64_t padded_count,
+                       const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream);
+
+/*
+ * The same product for bfloat16: values, x and y hold bf16 bits instead of fp16 bits (the MACKO layout does
+ * not depend on what the 16 bits of a stored value mean: the compressor only tests them for +-0 and
+ * canonicalises NaNs, see macko_compress_emit_bf16), products are exact, accumulation is fp32, y is rounded
+ * to bf16. The reference lists further value types as wanted (README.md:167) and ships fp16 and int8 kernels
+ * (src/macko_spmv/cuda/kernels.cuh:34-124,127-216); it has no bf16 kernel.
+ */
+int macko_spmv_bf16(const void *values, const void *deltas, const int32_t *row_indices,
+                    int64_t rows, int64_t cols, int64_t padded_count,
+                    const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream);
+
+/*
  * Same product with the kernel shape chosen by the caller, for tuning sweeps:
  *   lanes_per_row in {4, 8, 16, 32}; steps_in_flight in {2, 4, 6};
  *   x_in_shared 0/1; ctas_per_sm >= 1 (0 = library default).
@@ -88,6 +118,49 @@ int macko_spmv_fp16_tuned(const void *values, const void *deltas, const int32_t 
  */
 int macko_spmv_shape(int64_t rows, int64_t cols, int64_t padded_count, int sm_count,
                      int *lanes_per_row, int *steps_in_flight);
+
+/*
+ * Planned launch, for matrices whose rows are very long or very uneven. A plan is side metadata built once
+ * per matrix on the GPU from row_indices and deltas; the three MACKO buffers are not modified and stay what
+ * the reference format defines. It cuts every row into virtual rows of at most `segment_elements` stored
+ * elements (0 = default 1024; a multiple of 256, at most 3840), records for each where the decode has to
+ * resume (the column sum in front of the segment), sorts them by length and deals them to the warps longest
+ * first, so that every warp gets the same number of stored elements whatever the row lengths are. The
+ * segments of a cut row leave fp32 partial sums inside the plan; the segment that finishes last adds them up
+ * in segment order, so y is reproducible from call to call. Results match macko_spmv_fp16 up to the order of
+ * the fp32 additions.
+ *
+ *   macko_spmv_plan_bytes  size of the plan buffer for a matrix (-1 for arguments a plan cannot index)
+ *   macko_spmv_plan        builds the plan into `plan` (device memory, 16-byte aligned) and fills `info`
+ *                          (host memory); SYNCHRONISES `stream` once to read the counts back
+ *   macko_spmv_fp16_planned  the product; `info` is the structure macko_spmv_plan filled for this matrix.
+ *                          cols must fit shared memory (about 116 000). Calls that use one plan must not
+ *                          overlap on the GPU (they share the partial sums inside it).
+ * info->recommended is 1 when the row statistics say that the planned launch should beat macko_spmv_fp16
+ * (rows cut into several segments and much longer than the average row).
+ * No counterpart in the reference: its kernel gives every row one warp (kernels_torch_launchers.cuh:15-16),
+ * which is what makes uneven rows slow there.
+ */
+typedef struct macko_spmv_plan_info {
+    int64_t plan_bytes;       /* bytes of the plan buffer this info belongs to */
+    int64_t rows;
+    int64_t padded_count;
+    int32_t virtual_rows;
+    int32_t segment_elements;
+    int32_t longest_row;      /* stored elements of the longest row */
+    int32_t split_rows;       /* rows cut into more than one segment */
+    int32_t recommended;
+    int32_t reserved[3];
+} macko_spmv_plan_info;
+
+int64_t macko_spmv_plan_bytes(int64_t rows, int64_t cols, int64_t padded_count, int32_t segment_elements);
+int macko_spmv_plan(const void *deltas, const int32_t *row_indices, int64_t rows, int64_t cols,
+                    int64_t padded_count, int32_t segment_elements, void *plan, int64_t plan_bytes,
+                    macko_spmv_plan_info *info, void *stream);
+int macko_spmv_fp16_planned(const void *values, const void *deltas, const int32_t *row_indices,
+                            int64_t rows, int64_t cols, int64_t padded_count,
+                            const void *plan, const macko_spmv_plan_info *info,
+                            const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream);
 
 /*
  * Y = alpha * M X + beta * Y for `batch` right-hand sides at once: x is [batch][cols] and y is
@@ -150,6 +223,17 @@ int macko_compress_emit(const void *dense, int64_t rows, int64_t cols,
                         void *workspace, int64_t workspace_bytes, void *stream);
 
 /*
+ * macko_compress_emit for a matrix of bfloat16 values. The count phase is the same call for both types (it
+ * only tests the 16 bits for +-0, which fp16 and bf16 share); this phase differs in what counts as a NaN
+ * (bits above 0x7f80 instead of 0x7c00; every NaN is stored as 0x7fff, a quiet NaN in either type). The
+ * reference has no bf16 path (README.md:167 lists more value types as wanted); the layout is its fp16 layout.
+ */
+int macko_compress_emit_bf16(const void *dense, int64_t rows, int64_t cols,
+                             const int32_t *row_indices, int64_t padded_count,
+                             void *values, void *deltas,
+                             void *workspace, int64_t workspace_bytes, void *stream);
+
+/*
  * macko_compress_emit without a workspace argument, for hosts that cannot hand the library any
  * scratch memory: a plug-in running inside an application that has already given every byte of
  * device memory to its own pool, or a code path on which a cudaMalloc (which may stall the whole
@@ -174,6 +258,16 @@ int macko_compress_emit_static(const void *dense, int64_t rows, int64_t cols,
 
 /* Largest padded_count macko_compress_emit_static accepts. */
 int64_t macko_compress_static_capacity(void);
+
+/*
+ * Both emit entry points check every store on the device against padded_count: a call whose row_indices
+ * do not belong to the padded_count it passes (a stale P, or a matrix that changed between count and
+ * emit) writes nothing outside values[0, P) / the scratch, leaves the outputs incomplete and counts the
+ * warps that had to drop a store in a per-device counter. This call copies that counter to *count
+ * (0 = every emit since the last call was complete) and clears it; it synchronises `stream`.
+ * The reference over-allocates rows*cols + 8 slots for the same purpose (cpu_compressor.cuh:13-14).
+ */
+int macko_compress_overflow(uint32_t *count, void *stream);
 
 /*
  * Row-sharded product with the exchange fused into the kernel (several GPUs, one process each).
@@ -204,6 +298,24 @@ int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_
                             void *const *peer_y, int64_t row_offset, uint32_t *const *peer_flags,
                             int rank, int world, void *stream);
 int macko_peer_wait(uint32_t *local_flags, int world, void *stream);
+
+/*
+ * The same two calls with their options spelled out.
+ *   flags       MACKO_SPMV_MATRIX_IMMUTABLE, MACKO_SCATTER_DEFERRED_WAIT
+ *   spin_limit  polls of an arrival counter before a wait gives up (0 = default, 2^23: a few seconds)
+ * With MACKO_SCATTER_DEFERRED_WAIT the kernel forwards this rank's slice, publishes its arrival counter and
+ * ends; it overlaps with the next kernel of the stream like an ordinary product. Nothing may read the full
+ * y before a macko_peer_wait(_limited) enqueued after the last such product has run: it waits until every
+ * rank's arrival counter has reached this rank's call counter. A y buffer may be reused for a later product
+ * only after a wait that every rank has passed since its last use (e.g. alternate two sets of buffers from
+ * one wait to the next), because a faster rank writes its slice as soon as its own product is done.
+ * A wait that runs out sets flags[world + 2] = 1 + the missing rank and returns; the stream carries on.
+ */
+int macko_spmv_fp16_scatter_ex(const void *values, const void *deltas, const int32_t *row_indices,
+                               int64_t rows, int64_t cols, int64_t padded_count, const void *x,
+                               void *const *peer_y, int64_t row_offset, uint32_t *const *peer_flags,
+                               int rank, int world, uint32_t flags, uint32_t spin_limit, void *stream);
+int macko_peer_wait_limited(uint32_t *local_flags, int world, uint32_t spin_limit, void *stream);
 
 #ifdef __cplusplus
 }

@@ -86,6 +86,16 @@ def _decompress_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols):
     return torch.empty((M_rows, M_cols), device=M_values.device, dtype=M_values.dtype)
 
 
+@torch.library.register_fake("macko_spmv::multiply_frozen")
+def _multiply_frozen_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, V):
+    return torch.empty((M_rows,), device=M_values.device, dtype=M_values.dtype)
+
+
+@torch.library.register_fake("macko_spmv::multiply_planned")
+def _multiply_planned_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, plan, virtual_rows, segment_elements, V, frozen):
+    return torch.empty((M_rows,), device=M_values.device, dtype=M_values.dtype)
+
+
 def move_to_device(compressed, device):
     """Move the three buffers of a compressed matrix (src/macko_spmv/__init__.py:110-117)."""
     return (
@@ -118,6 +128,42 @@ def compress(M):
         raise NotImplementedError()
 
 
+class FrozenMatrix(tuple):
+    """The 5-tuple of `compress` for a matrix that will not be written any more (weights), as returned by
+    `freeze`. `multiply` recognises it and lets the kernel fetch matrix data while the previous kernel of
+    the stream is still finishing; with a plan (see `freeze`) it runs the planned launch. It is still a
+    tuple of the same five items, so everything that takes the reference's compressed object takes it."""
+
+    plan = None        # device buffer of the plan, or None
+    plan_meta = None   # (virtual_rows, segment_elements, longest_row, split_rows, recommended)
+
+    def __new__(cls, compressed, plan=None, plan_meta=None):
+        self = super().__new__(cls, tuple(compressed[:5]))
+        self.plan = plan
+        self.plan_meta = plan_meta
+        return self
+
+
+def freeze(compressed_M, plan="auto", segment_elements=0):
+    """Declare a compressed CUDA matrix immutable and, if it pays, build its launch plan.
+
+    Waits once for the device work that produced the buffers (they must be complete before a kernel may read
+    them ahead of stream order). `plan`: "auto" builds the plan and keeps it only if the row statistics
+    recommend it (rows far longer than the average, e.g. skewed matrices), True keeps it always, False builds
+    none. The reference has no counterpart (src/macko_spmv/__init__.py has only compress / multiply)."""
+    assert compressed_M[0].is_cuda and compressed_M[1].is_cuda and compressed_M[2].is_cuda
+    torch.cuda.synchronize(compressed_M[0].device)
+    if plan is False or compressed_M[0].dtype != torch.float16:
+        return FrozenMatrix(compressed_M)
+    buf, meta = torch.ops.macko_spmv.plan_build.default(
+        compressed_M[1], compressed_M[2], compressed_M[3], compressed_M[4], compressed_M[0].numel(), int(segment_elements))
+    meta = [int(v) for v in meta.tolist()]
+    info = (meta[3], meta[4], meta[5], meta[6], meta[7])
+    if plan is True or info[4]:
+        return FrozenMatrix(compressed_M, buf, info)
+    return FrozenMatrix(compressed_M, None, info)
+
+
 def multiply(compressed_M, V):
     """y = M @ V for a compressed matrix and an fp16 CUDA vector (src/macko_spmv/__init__.py:134-149)."""
     assert compressed_M[0].is_cuda
@@ -125,6 +171,13 @@ def multiply(compressed_M, V):
     assert compressed_M[2].is_cuda
     assert V.is_cuda
     assert V.is_contiguous()
+    if isinstance(compressed_M, FrozenMatrix):
+        if compressed_M.plan is not None:
+            return torch.ops.macko_spmv.multiply_planned.default(
+                compressed_M[0], compressed_M[1], compressed_M[2], compressed_M[3], compressed_M[4],
+                compressed_M.plan, compressed_M.plan_meta[0], compressed_M.plan_meta[1], V, True)
+        return torch.ops.macko_spmv.multiply_frozen.default(
+            compressed_M[0], compressed_M[1], compressed_M[2], compressed_M[3], compressed_M[4], V)
     return torch.ops.macko_spmv.multiply.default(
         compressed_M[0],
         compressed_M[1],
@@ -163,4 +216,5 @@ def multiply_batched(compressed_M, V):
     return torch.ops.macko_spmv.multiply_batched.default(*compressed_M[:5], V)
 
 
-__all__ = ["compress", "multiply", "multiply_batched", "decompress", "move_to_device", "native_library_paths", "native_version", "LIB_NAME"]
+__all__ = ["compress", "multiply", "multiply_batched", "decompress", "move_to_device", "freeze", "FrozenMatrix",
+           "native_library_paths", "native_version", "LIB_NAME"]

@@ -21,7 +21,7 @@ LIB_CORE = os.path.join(PKG_DIR, "libmacko_b200.so")
 LIB_TORCH = os.path.join(PKG_DIR, "_torch_ops.so")
 BENCH_CLI = os.path.join(PKG_DIR, "macko_bench")
 
-CUDA_SOURCES = ["common.cu", "spmv.cu", "compress.cu", "decompress.cu"]
+CUDA_SOURCES = ["common.cu", "spmv.cu", "compress.cu", "decompress.cu", "plan.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
@@ -52,7 +52,7 @@ def _nvcc() -> str:
 
 
 def build_core(force: bool = False, verbose: bool = False) -> str:
-    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(INCLUDE, "macko_b200.h")]
+    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "plan.cuh"), os.path.join(INCLUDE, "macko_b200.h")]
     sources = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
     if not force and _newer(LIB_CORE, sources + headers + [__file__]):
         return LIB_CORE

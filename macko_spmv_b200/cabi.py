@@ -23,12 +23,34 @@ _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
 _f = ctypes.c_float
 _int = ctypes.c_int
+_u32 = ctypes.c_uint32
+_i32 = ctypes.c_int32
+
+# flag bits (include/macko_b200.h)
+SPMV_MATRIX_IMMUTABLE = 1
+SCATTER_DEFERRED_WAIT = 2
+
+
+class PlanInfo(ctypes.Structure):
+    """``macko_spmv_plan_info``: what ``macko_spmv_plan`` reports and ``macko_spmv_fp16_planned`` takes back."""
+
+    _fields_ = [
+        ("plan_bytes", _i64), ("rows", _i64), ("padded_count", _i64),
+        ("virtual_rows", _i32), ("segment_elements", _i32), ("longest_row", _i32), ("split_rows", _i32),
+        ("recommended", _i32), ("reserved", _i32 * 3),
+    ]
+
 
 SIGNATURES = {
     "macko_version": (_int, []),
     "macko_status_string": (ctypes.c_char_p, [_int]),
     "macko_last_error": (ctypes.c_char_p, []),
     "macko_spmv_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp]),
+    "macko_spmv_fp16_ex": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _u32, _vp]),
+    "macko_spmv_bf16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _u32, _vp]),
+    "macko_spmv_plan_bytes": (_i64, [_i64, _i64, _i64, _i32]),
+    "macko_spmv_plan": (_int, [_vp, _vp, _i64, _i64, _i64, _i32, _vp, _i64, ctypes.POINTER(PlanInfo), _vp]),
+    "macko_spmv_fp16_planned": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, ctypes.POINTER(PlanInfo), _vp, _vp, _f, _f, _u32, _vp]),
     "macko_spmv_fp16_tuned": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp, _int, _int, _int, _int]),
     "macko_spmv_shape": (_int, [_i64, _i64, _i64, _int, _vp, _vp]),
     "macko_spmm_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _f, _f, _vp]),
@@ -36,10 +58,14 @@ SIGNATURES = {
     "macko_compress_count": (_int, [_vp, _i64, _i64, _vp, _vp]),
     "macko_compress_workspace_bytes": (_i64, [_i64]),
     "macko_compress_emit": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "macko_compress_emit_bf16": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
     "macko_compress_emit_static": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "macko_compress_static_capacity": (_i64, []),
+    "macko_compress_overflow": (_int, [ctypes.POINTER(_u32), _vp]),
     "macko_spmv_fp16_scatter": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _int, _int, _vp]),
     "macko_peer_wait": (_int, [_vp, _int, _vp]),
+    "macko_spmv_fp16_scatter_ex": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _int, _int, _u32, _u32, _vp]),
+    "macko_peer_wait_limited": (_int, [_vp, _int, _u32, _vp]),
 }
 
 

@@ -25,6 +25,10 @@ struct DeviceInfo {
 // Attributes of the current device, queried once per device.
 int current_device_info(const DeviceInfo **out);
 
+// In-place inclusive prefix sum over counts[1..rows] with counts[0] = 0 (one CTA; defined in compress.cu,
+// shared by the compressor and the plan builder).
+int launch_row_scan(int *counts, int rows, cudaStream_t stream);
+
 inline bool aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 }  // namespace macko

@@ -29,9 +29,16 @@ constexpr int kColsPerStep = 32 * kColsPerLane;
 constexpr int kUnroll = 4;        // steps whose loads are in flight together
 constexpr int kStageElems = 320;  // stored elements of one step that fit the per-warp staging area
 
-__device__ __forceinline__ unsigned short canonical(unsigned short h)
+// Warps of the emit kernel (and the pack kernel) that had to refuse a store because row_indices pointed
+// beyond the padded count they were given: non-zero means that the outputs of that call are incomplete.
+// Per device, read and cleared by macko_compress_overflow().
+static __device__ unsigned g_compress_overflow;
+
+// Every NaN is stored as 0x7fff (what the reference's float round trip makes of it, cpu_compressor.cuh:26,36).
+// `nan_above` is the bit pattern of +infinity of the value type: 0x7c00 for fp16, 0x7f80 for bfloat16.
+__device__ __forceinline__ unsigned short canonical(unsigned short h, unsigned nan_above)
 {
-    return ((h & 0x7fffu) > 0x7c00u) ? (unsigned short)0x7fffu : h;
+    return ((h & 0x7fffu) > nan_above) ? (unsigned short)0x7fffu : h;
 }
 
 // Loads the 8 fp16 of this lane for the step starting at global element index g0 (a multiple of 8
@@ -88,7 +95,9 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
                      int *__restrict__ row_counts_out,           // !EMIT: count of row r at [r+1]
                      const int *__restrict__ row_indices,        // EMIT
                      unsigned short *__restrict__ values,        // EMIT
-                     unsigned char *__restrict__ nibbles)        // EMIT: one delta per byte
+                     unsigned char *__restrict__ nibbles,        // EMIT: one delta per byte
+                     int limit,                                  // EMIT: slots in values / nibbles (P)
+                     unsigned nan_above)                         // EMIT: +infinity of the value type
 {
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
@@ -102,6 +111,10 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
     int carry_prev = -1;   // column of the last non-zero seen so far in this row
     int count = 0;         // !EMIT: stored elements seen by this lane
     int out = EMIT ? row_indices[row] : 0;  // EMIT: next output slot of the warp
+    // EMIT: output slots come from row_indices, which the caller may have paired with a too small P (or
+    // with a matrix that changed since the count): every store is checked against `limit` and refused
+    // stores are counted, so an inconsistent call cannot write outside values / the scratch.
+    bool refused = false;
 
     // EMIT: the stored elements of one step are gathered in shared memory and written out with
     // coalesced stores (every lane writing its own few elements would issue many tiny stores).
@@ -145,17 +158,27 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
                 int k = staged ? incl - mine : out + incl - mine;
                 unsigned short *vdst = staged ? stage_v[wslot] : values;
                 unsigned char *ndst = staged ? stage_n[wslot] : nibbles;
+                // staged slots are below step_total <= kStageElems by construction; direct slots are checked
+                const unsigned cap = staged ? (unsigned)kStageElems : (unsigned)limit;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     if (nz & (1u << i)) {
                         const int c = c0 + i;
                         for (int p = prev + 16; p < c; p += 16) {  // pads keep the sign of the zero they sit on
-                            vdst[k] = __ldg(dense + row_lo + p);
-                            ndst[k] = 15;
+                            if ((unsigned)k < cap) {
+                                vdst[k] = __ldg(dense + row_lo + p);
+                                ndst[k] = 15;
+                            } else {
+                                refused = true;
+                            }
                             ++k;
                         }
-                        vdst[k] = canonical((unsigned short)((w[i >> 1] >> (16 * (i & 1))) & 0xffffu));
-                        ndst[k] = (unsigned char)((c - prev - 1) & 15);
+                        if ((unsigned)k < cap) {
+                            vdst[k] = canonical((unsigned short)((w[i >> 1] >> (16 * (i & 1))) & 0xffffu), nan_above);
+                            ndst[k] = (unsigned char)((c - prev - 1) & 15);
+                        } else {
+                            refused = true;
+                        }
                         ++k;
                         prev = c;
                     }
@@ -163,8 +186,12 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
                 if (staged) {
                     __syncwarp();
                     for (int i = lane; i < step_total; i += 32) {
-                        values[out + i] = stage_v[wslot][i];
-                        nibbles[out + i] = stage_n[wslot][i];
+                        if ((unsigned)(out + i) < (unsigned)limit) {
+                            values[out + i] = stage_v[wslot][i];
+                            nibbles[out + i] = stage_n[wslot][i];
+                        } else {
+                            refused = true;
+                        }
                     }
                     __syncwarp();
                 }
@@ -176,6 +203,8 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
         if (lane == 0) row_counts_out[row + 1] = count;
+    } else {
+        if (__any_sync(0xffffffffu, refused) && lane == 0) atomicAdd(&g_compress_overflow, 1u);
     }
 }
 
@@ -234,8 +263,9 @@ pack_kernel(const uint2 *__restrict__ nibbles8, const int *__restrict__ ri, int 
             unsigned *__restrict__ deltas32, unsigned short *__restrict__ values)
 {
     const int g = blockIdx.x * 256 + threadIdx.x;
-    if (g >= groups) return;
+    if (g >= groups) return;   // every read and write below stays under 8 * groups = P
     const int n = ri[rows];
+    if (g == 0 && (n < 0 || n > 8 * groups)) atomicAdd(&g_compress_overflow, 1u);   // row_indices and P do not belong together
     const int k0 = g * 8;
     unsigned packed = 0;
     if (k0 < n) {
@@ -304,6 +334,13 @@ int static_scratch_address(unsigned char **out)
 }
 
 }  // namespace
+
+int launch_row_scan(int *counts, int rows, cudaStream_t stream)
+{
+    scan_rows_kernel<<<1, 1024, 0, stream>>>(counts, rows);
+    return launch_error("row scan launch");
+}
+
 }  // namespace macko
 
 extern "C" {
@@ -320,19 +357,18 @@ int macko_compress_count(const void *dense, int64_t rows, int64_t cols, int32_t 
         const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
         compress_rows_kernel<false><<<grid, kThreads, 0, s>>>(
             static_cast<const unsigned short *>(dense), (int)rows, (int)cols, aligned(dense, 16),
-            row_indices, nullptr, nullptr, nullptr);
+            row_indices, nullptr, nullptr, nullptr, 0, 0u);
         st = launch_error("compress count launch");
         if (st != MACKO_OK) return st;
     }
-    scan_rows_kernel<<<1, 1024, 0, s>>>(row_indices, (int)rows);
-    return launch_error("row scan launch");
+    return launch_row_scan(row_indices, (int)rows, s);
 }
 
 int64_t macko_compress_workspace_bytes(int64_t padded_count) { return padded_count < 0 ? 0 : padded_count; }
 
-int macko_compress_emit(const void *dense, int64_t rows, int64_t cols, const int32_t *row_indices,
-                        int64_t padded_count, void *values, void *deltas,
-                        void *workspace, int64_t workspace_bytes, void *stream)
+static int compress_emit_typed(const void *dense, int64_t rows, int64_t cols, const int32_t *row_indices,
+                               int64_t padded_count, void *values, void *deltas,
+                               void *workspace, int64_t workspace_bytes, void *stream, unsigned nan_above)
 {
     using namespace macko;
     int st = check_dense(dense, rows, cols);
@@ -352,7 +388,8 @@ int macko_compress_emit(const void *dense, int64_t rows, int64_t cols, const int
         const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
         compress_rows_kernel<true><<<grid, kThreads, 0, s>>>(
             static_cast<const unsigned short *>(dense), (int)rows, (int)cols, aligned(dense, 16),
-            nullptr, row_indices, static_cast<unsigned short *>(values), static_cast<unsigned char *>(workspace));
+            nullptr, row_indices, static_cast<unsigned short *>(values), static_cast<unsigned char *>(workspace),
+            (int)padded_count, nan_above);
         st = launch_error("compress emit launch");
         if (st != MACKO_OK) return st;
     }
@@ -361,6 +398,40 @@ int macko_compress_emit(const void *dense, int64_t rows, int64_t cols, const int
         static_cast<const uint2 *>(workspace), row_indices, (int)rows, groups,
         static_cast<unsigned *>(deltas), static_cast<unsigned short *>(values));
     return launch_error("pack launch");
+}
+
+int macko_compress_emit(const void *dense, int64_t rows, int64_t cols, const int32_t *row_indices,
+                        int64_t padded_count, void *values, void *deltas,
+                        void *workspace, int64_t workspace_bytes, void *stream)
+{
+    return compress_emit_typed(dense, rows, cols, row_indices, padded_count, values, deltas, workspace, workspace_bytes,
+                               stream, 0x7c00u);
+}
+
+int macko_compress_emit_bf16(const void *dense, int64_t rows, int64_t cols, const int32_t *row_indices,
+                             int64_t padded_count, void *values, void *deltas,
+                             void *workspace, int64_t workspace_bytes, void *stream)
+{
+    return compress_emit_typed(dense, rows, cols, row_indices, padded_count, values, deltas, workspace, workspace_bytes,
+                               stream, 0x7f80u);
+}
+
+int macko_compress_overflow(uint32_t *count, void *stream)
+{
+    using namespace macko;
+    if (!count) return fail(MACKO_ERR_INVALID_ARGUMENT, "null count");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned seen = 0;
+    cudaError_t e = cudaMemcpyFromSymbolAsync(&seen, g_compress_overflow, sizeof(seen), 0, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess && seen != 0) {
+        const unsigned zero = 0;
+        e = cudaMemcpyToSymbolAsync(g_compress_overflow, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    }
+    if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "reading the compressor's overflow word: %s", cudaGetErrorString(e));
+    *count = seen;
+    return MACKO_OK;
 }
 
 int64_t macko_compress_static_capacity(void) { return macko::kStaticScratchBytes; }
@@ -393,7 +464,7 @@ int macko_compress_emit_static(const void *dense, int64_t rows, int64_t cols, co
         const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
         compress_rows_kernel<true><<<grid, kThreads, 0, s>>>(
             static_cast<const unsigned short *>(dense), (int)rows, (int)cols, aligned(dense, 16),
-            nullptr, row_indices, static_cast<unsigned short *>(values), scratch);
+            nullptr, row_indices, static_cast<unsigned short *>(values), scratch, (int)padded_count, 0x7c00u);
         st = launch_error("compress emit (static scratch) launch");
         if (st != MACKO_OK) return st;
     }

@@ -22,9 +22,17 @@
 //     zero-framed copy (masked-out elements read 0 without range checks), and the sm_100
 //     fp16 x fp16 + fp32 fused multiply-add needs no conversions;
 //   * row boundaries that fall inside a unit are handled by masking that unit, only in warps
-//     that actually contain such a unit (one warp-wide reduction per iteration finds them).
+//     that actually contain such a unit (one warp-wide reduction per iteration finds them);
+//   * the first matrix loads of every warp are in flight before x is staged, and, when the caller
+//     declares the matrix immutable, before the kernel waits for the previous kernel of the stream
+//     (programmatic dependent launch), so the first HBM round trip overlaps that kernel's tail;
+//   * a planned launch walks "virtual rows" (rows cut into segments of bounded length, sorted by
+//     length and dealt to the warps in serpentine order) from side metadata built once per matrix,
+//     which balances matrices with very uneven rows; the compressed buffers stay untouched.
 #include "common.cuh"
+#include "plan.cuh"
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <cstdlib>
@@ -41,16 +49,39 @@ constexpr int kXPadBack = 160;       // zero fp16 slots after x[cols-1]  (> 8 * 
 // acc += fp16(low or high half of vword) * fp16(low half of xbits): the sm_100 mixed-precision FMA
 // (exact fp16 product accumulated in fp32, round to nearest); the halves are split inside the asm so
 // that no repacking instructions are needed around it.
-template <int HALF>
+template <int HALF, bool BF = false>
 __device__ __forceinline__ float fma_h(float acc, unsigned vword, unsigned xbits)
 {
-    if (HALF)
-        asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, h, xl, %0;}"
-            : "+f"(acc) : "r"(vword), "r"(xbits));
-    else
-        asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, l, xl, %0;}"
-            : "+f"(acc) : "r"(vword), "r"(xbits));
+    if (BF) {
+        if (HALF)
+            asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.bf16 %0, h, xl, %0;}"
+                : "+f"(acc) : "r"(vword), "r"(xbits));
+        else
+            asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.bf16 %0, l, xl, %0;}"
+                : "+f"(acc) : "r"(vword), "r"(xbits));
+    } else {
+        if (HALF)
+            asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, h, xl, %0;}"
+                : "+f"(acc) : "r"(vword), "r"(xbits));
+        else
+            asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.f16 %0, l, xl, %0;}"
+                : "+f"(acc) : "r"(vword), "r"(xbits));
+    }
     return acc;
+}
+
+// 16-bit storage type <-> fp32 for the y epilogue (fp16 or bf16 bits in an unsigned short)
+template <bool BF>
+__device__ __forceinline__ unsigned short to_bits16(float f)
+{
+    if (BF) return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+    return __half_as_ushort(__float2half_rn(f));
+}
+template <bool BF>
+__device__ __forceinline__ float from_bits16(unsigned short b)
+{
+    if (BF) return __bfloat162float(__ushort_as_bfloat16(b));
+    return __half2float(__ushort_as_half(b));
 }
 
 // acc += fp16(half VH of vword) * fp16(half XH of xword)
@@ -131,13 +162,56 @@ __device__ __forceinline__ void mask_unit(uint4 &v, unsigned &w, int lo, int hi)
 // device pointers) and every rank's flag words. world == 0 for an ordinary launch.
 template <int V> struct Int { static constexpr int value = V; };
 
+// A virtual row of a planned launch is done (called by the leader lane of its group): a whole row goes to
+// y; a segment of a long row leaves its fp32 sum in the plan, and the segment that finds all others of its
+// row delivered adds them up in segment order, so the result does not depend on who finishes last.
+__device__ __forceinline__ void plan_row_done(const PlanView &pl, unsigned o, float total, float alpha, float beta,
+                                              unsigned short *__restrict__ y16, int rows)
+{
+    if (!(o & kPlanPartialBit)) {
+        if (o < (unsigned)rows) {
+            float r = alpha * total;
+            if (beta != 0.f) r += beta * __half2float(__ushort_as_half(y16[o]));
+            y16[o] = __half_as_ushort(__float2half_rn(r));
+        }
+        return;
+    }
+    const unsigned v = o & ~kPlanPartialBit;
+    if (v >= (unsigned)pl.n_virtual) return;
+    const unsigned row = __ldg(pl.vrow + v);
+    if (row >= (unsigned)rows) return;
+    const int first = __ldg(pl.seg_first + row);
+    const int n = __ldg(pl.seg_first + row + 1) - first;
+    __stcg(pl.partial + v, total);
+    __threadfence();   // the partial sum is visible device-wide before this segment counts as delivered
+    const unsigned before = atomicAdd(pl.arrived + row, 1u);
+    if ((int)before == n - 1) {
+        __threadfence();   // every segment counted before this one has its partial sum visible
+        float sum = 0.f;
+        for (int i = 0; i < n; ++i) sum += __ldcg(pl.partial + first + i);
+        float r = alpha * sum;
+        if (beta != 0.f) r += beta * __half2float(__ushort_as_half(y16[row]));
+        y16[row] = __half_as_ushort(__float2half_rn(r));
+        pl.arrived[row] = 0u;   // ready for the next launch with this plan
+    }
+}
+
 constexpr int kMaxPeers = 8;
+constexpr unsigned kDefaultSpinLimit = 1u << 23;
 struct Peers {
     __half *y[kMaxPeers];
     unsigned *flags[kMaxPeers];   // per rank: [0, world) arrival counters, [world] calls issued, [world+1] CTA ticket, [world+2] error
     long long row_offset;         // first row of this rank's block in the full y
     int world;
     int rank;
+    unsigned spin_limit;          // polls of the arrival counters before the wait gives up
+    int deferred;                 // publish and return: the caller enqueues macko_peer_wait where y is consumed
+};
+
+// What a launch carries besides the reference's arguments.
+struct Extra {
+    unsigned flags;               // MACKO_SPMV_MATRIX_IMMUTABLE
+    PlanView plan;                // planned launch: virtual rows instead of row_indices (PLAN kernels only)
 };
 
 // L     lanes per row (a warp walks 32/L rows at once)
@@ -149,13 +223,18 @@ struct Peers {
 // BV    vectors multiplied at once (1, 2, 4 or 8): x is [batch][cols] and y is [batch][rows], batch <= BV.
 //       The matrix is streamed once; shared memory holds the vectors interleaved (BV values per column),
 //       so one vector load gathers a column of all of them.
-template <int L, int NPAIR, bool XS, bool PEER, int BV = 1>
+// PLAN  rows come from a plan: virtual rows (begin, length, starting column, destination) sorted by length;
+//       the segments of a long row leave fp32 partial sums that the last one to finish adds up in segment order
+// BF    values, x and y are bfloat16 instead of fp16 (same buffers, same decode; fp32 accumulation either way)
+template <int L, int NPAIR, bool XS, bool PEER, int BV = 1, bool PLAN = false, bool BF = false>
 __global__ void __launch_bounds__(kThreads, 2)
 spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
             const int *__restrict__ ri, const __half *__restrict__ x, __half *__restrict__ y,
-            int rows, int cols, int stored, float alpha, float beta, const Peers peers, int batch)
+            int rows, int cols, int stored, float alpha, float beta, const Peers peers, int batch, const Extra extra)
 {
     static_assert(BV == 1 || (XS && !PEER), "batched products gather from shared memory and have no scatter epilogue");
+    static_assert(!PLAN || (XS && !PEER && BV == 1), "planned launches are built for the single-vector product with x in shared memory");
+    static_assert(!BF || (!PEER && BV == 1 && !PLAN), "bfloat16 is built for the plain single-vector product");
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int STEP = kGroup * L;   // elements per group per sub-step
     constexpr int D = 2 * NPAIR;       // sub-steps per iteration
@@ -165,74 +244,87 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     const int lig = lane & (L - 1);          // lane in group
     const int group_lane0 = lane & ~(L - 1); // first lane of my group
     constexpr unsigned kLeaders = (L == 32) ? 0x1u : (L == 16) ? 0x00010001u : (L == 8) ? 0x01010101u : 0x11111111u;
+    unsigned short *y16 = reinterpret_cast<unsigned short *>(y);
 
     // Programmatic dependent launch: let the next kernel of the stream start occupying SMs as ours
-    // drain, and do not touch memory before every earlier kernel of the stream has completed (the
-    // matrix, x and y may all have been produced by them). Both are no-ops for a plain launch.
+    // drain. Memory written by earlier kernels of the stream (x, y, and the matrix unless the caller has
+    // declared it immutable) is not touched before griddepcontrol.wait. Both are no-ops for a plain launch.
     asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const bool matrix_early = (extra.flags & MACKO_SPMV_MATRIX_IMMUTABLE) != 0u;
+    if (!matrix_early) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // ---- this warp's contiguous row range, dealt in blocks of K rows so that the groups of a warp
-    //      run out of rows together ------------------------------------------------------------------
+    // ---- this warp's work: a contiguous row range dealt in blocks of K rows (so that the groups of a warp
+    //      run out of rows together), or, planned, every n_warps-th block of K virtual rows of the sorted
+    //      list, the direction alternating from round to round (longest first: the ends even out) ------------
     const long long n_warps = (long long)gridDim.x * kWarpsPerCta;
     const long long warp_id = (long long)blockIdx.x * kWarpsPerCta + (tid >> 5);
-    const long long n_blocks = ((long long)rows + K - 1) / K;
-    int row_next = (int)min((long long)rows, (n_blocks * warp_id / n_warps) * K);
-    const int row_hi = (int)min((long long)rows, (n_blocks * (warp_id + 1) / n_warps) * K);
+    int row_next, row_hi;   // plain: rows [row_next, row_hi); planned: positions in the warp's sequence
+    if constexpr (PLAN) {
+        const int V = extra.plan.n_virtual;
+        const int W = (int)n_warps, w = (int)warp_id;
+        const int nb = (V + K - 1) / K;                 // blocks of K virtual rows
+        const int full_rounds = nb / W;
+        const int rest = nb - full_rounds * W;           // blocks of the last, partly filled round
+        const int slot = (full_rounds & 1) ? W - 1 - w : w;
+        const int count = full_rounds + (slot < rest ? 1 : 0);
+        row_next = 0;
+        row_hi = count * K;
+        if (count > 0) {
+            const int last_round = count - 1;
+            const int last_blk = last_round * W + ((last_round & 1) ? W - 1 - w : w);
+            if (last_blk == nb - 1) row_hi -= nb * K - V;   // the very last block may hold fewer than K
+        }
+    } else {
+        const long long n_blocks = ((long long)rows + K - 1) / K;
+        row_next = (int)min((long long)rows, (n_blocks * warp_id / n_warps) * K);
+        row_hi = (int)min((long long)rows, (n_blocks * (warp_id + 1) / n_warps) * K);
+    }
+    // sorted index of position p of this warp's sequence (planned)
+    auto sorted_index = [&](int p) -> int {
+        const int W = (int)n_warps, w = (int)warp_id;
+        const int round = p / K;
+        return (round * W + ((round & 1) ? W - 1 - w : w)) * K + (p - round * K);
+    };
 
     // PEER: rows of the whole CTA (its warps own consecutive ranges) and the staging area for their y
-    const long long cta_w0 = (long long)blockIdx.x * kWarpsPerCta;
-    const int cta_row_lo = (int)min((long long)rows, (n_blocks * cta_w0 / n_warps) * K);
-    const int cta_row_hi = (int)min((long long)rows, (n_blocks * (cta_w0 + kWarpsPerCta) / n_warps) * K);
+    int cta_row_lo = 0, cta_row_hi = 0;
+    if constexpr (PEER) {
+        const long long n_blocks = ((long long)rows + K - 1) / K;
+        const long long cta_w0 = (long long)blockIdx.x * kWarpsPerCta;
+        cta_row_lo = (int)min((long long)rows, (n_blocks * cta_w0 / n_warps) * K);
+        cta_row_hi = (int)min((long long)rows, (n_blocks * (cta_w0 + kWarpsPerCta) / n_warps) * K);
+    }
     __half *ystage = reinterpret_cast<__half *>(smem + (((size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) + 15) & ~(size_t)15));
 
-    // Window of 32 row offsets held one per lane; entry r of the window is read by shuffle.
+    // Window of 32 row offsets (planned: 32 virtual-row descriptors) held one per lane and read by shuffle.
     int win_base = row_next;
-    int ri_reg = 0;
-    if (row_next < row_hi) ri_reg = __ldg(ri + min(win_base + lane, rows));
-
-    // ---- stage x into shared memory, framed by zeros ------------------------------------------------
-    int x_base = 0;  // shared-window byte address of the front padding
-    if (BV > 1) {
-        __half *xs = reinterpret_cast<__half *>(smem);
-        const int n_total = (kXPadFront + cols + kXPadBack) * BV;
-        for (int i = tid; i < kXPadFront * BV; i += kThreads) xs[i] = __ushort_as_half(0);
-        for (int i = (kXPadFront + cols) * BV + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
-#pragma unroll
-        for (int b = 0; b < BV; ++b) {
-            const __half *xb = x + (size_t)b * cols;
-            for (int c = tid; c < cols; c += kThreads)
-                xs[(size_t)(kXPadFront + c) * BV + b] = b < batch ? xb[c] : __ushort_as_half(0);
-        }
-        x_base = (int)__cvta_generic_to_shared(xs);
-        __syncthreads();
-    } else if (XS) {
-        __half *xs = reinterpret_cast<__half *>(smem);
-        const int n_total = kXPadFront + cols + kXPadBack;
-        for (int i = tid; i < kXPadFront; i += kThreads) xs[i] = __ushort_as_half(0);
-        for (int i = kXPadFront + cols + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
-        if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-            const uint4 *src = reinterpret_cast<const uint4 *>(x);
-            uint4 *dst = reinterpret_cast<uint4 *>(xs + kXPadFront);
-            const int n_vec = cols >> 3;
-            for (int i = tid; i < n_vec; i += kThreads) dst[i] = __ldg(src + i);
-            for (int i = (n_vec << 3) + tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
+    int ri_reg = 0;      // plain: ri[win_base + lane]; planned: first stored element of the virtual row
+    unsigned pk_reg = 0; // planned: length | starting column << kPlanLenBits
+    auto load_window = [&]() {
+        if constexpr (PLAN) {
+            const int p = win_base + lane;
+            uint2 d = make_uint2(0u, 0u);
+            if (p < row_hi) d = __ldg(extra.plan.desc + sorted_index(p));
+            ri_reg = (int)d.x;
+            pk_reg = d.y;
         } else {
-            for (int i = tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
+            ri_reg = __ldg(ri + min(win_base + lane, rows));
         }
-        x_base = (int)__cvta_generic_to_shared(xs);
-        __syncthreads();
-    }
+    };
+    if (row_next < row_hi) load_window();
 
     // ---- per-group state ------------------------------------------------------------------------------
     constexpr int LOG_STEP = (L == 32) ? 8 : (L == 16) ? 7 : (L == 8) ? 6 : 5;
-    int my_row = -1;   // row being walked by my group (-1: none)
+    int my_row = -1;   // plain: row being walked by my group (-1: none); planned: 0 while a virtual row is walked
+    unsigned out_word = 0u;   // planned: destination of the virtual row (a row of y, or a partial-sum slot)
     int begin = 0;     // first stored element of the row
     int end = 0;       // one past the last stored element
     int pos = 0;       // first element of the group's next iteration (multiple of 8)
     // Byte address (shared window, or byte offset from x - kXPadFront when x stays in global memory) of
     // "column -1 + index in row" in front of the lane's unit of the next sub-step, less 14 per lane below
     // it in the group: the lane totals that go through the scan carry +14 each (see the decode below).
+    // x_base (the shared-window address of the front padding) is known before x is staged.
+    const int x_base = (XS || BV > 1) ? (int)__cvta_generic_to_shared(smem) : 0;
     const int x_fold = (BV == 1) ? x_base : 0;   // batched: offsets stay per-vector and are scaled by BV at the gather
     const unsigned lane_const = (unsigned)(x_fold + 2 * kXPadFront + 2 * lig);
     const unsigned a_max = (unsigned)(x_fold + 2 * (kXPadFront + cols));
@@ -242,7 +334,9 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
 #pragma unroll
     for (int b = 0; b < BV; ++b) accb[b][0] = accb[b][1] = 0.f;
 
+    bool first_pass = true;
     for (;;) {
+        bool done = false;
         // ---- groups that ran out of work finish their row and take the next one ---------------------
         const bool need = pos >= end;
         const unsigned needmask = __ballot_sync(0xffffffffu, need);
@@ -253,12 +347,14 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 for (int o = L / 2; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
                 if (need) {
                     if (my_row >= 0 && lig == 0) {
-                        float r = alpha * total;
-                        if (PEER) {
-                            ystage[my_row - cta_row_lo] = __float2half_rn(r);   // delivered in bulk at the end
+                        if constexpr (PLAN) {
+                            plan_row_done(extra.plan, out_word, total, alpha, beta, y16, rows);
+                        } else if constexpr (PEER) {
+                            ystage[my_row - cta_row_lo] = __float2half_rn(alpha * total);   // delivered in bulk at the end
                         } else {
-                            if (beta != 0.f) r += beta * __half2float(y[my_row]);
-                            y[my_row] = __float2half_rn(r);
+                            float r = alpha * total;
+                            if (beta != 0.f) r += beta * from_bits16<BF>(y16[my_row]);
+                            y16[my_row] = to_bits16<BF>(r);
                         }
                     }
                     acc0 = acc1 = acc2 = acc3 = 0.f;
@@ -282,25 +378,41 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
             }
             const int avail = row_hi - row_next;
             if (avail <= 0) {
-                if (needmask == 0xffffffffu) break;
+                if (needmask == 0xffffffffu) done = true;
                 if (need) { my_row = -1; pos = 0; end = 0; begin = 0; }
             } else {
                 const unsigned leaders = needmask & kLeaders;
                 const int want = __popc(leaders);
                 const int take = min(want, avail);
-                if (row_next + take > win_base + 31) {  // warp-uniform
+                if (row_next + take > win_base + (PLAN ? 32 : 31)) {  // warp-uniform
                     win_base = row_next;
-                    ri_reg = __ldg(ri + min(win_base + lane, rows));
+                    load_window();
                 }
                 const int rank = __popc(leaders & ((1u << group_lane0) - 1u));
                 const int nr = row_next + rank;
-                // offsets are clamped into [0, stored] so that a corrupt row_indices cannot send loads outside values/deltas
-                const int b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
-                const int e = min(__shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31), stored);
+                // offsets are clamped into [0, stored] so that corrupt row_indices (or a corrupt plan) cannot send
+                // loads outside values/deltas
+                int b, e;
+                unsigned colbase2 = 0u;   // planned: twice the column sum in front of the segment (a byte offset into x)
+                if constexpr (PLAN) {
+                    b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
+                    const unsigned pk = __shfl_sync(0xffffffffu, pk_reg, (nr - win_base) & 31);
+                    e = min(b + (int)(pk & ((1u << kPlanLenBits) - 1u)), stored);
+                    colbase2 = (pk >> kPlanLenBits) << 1;
+                } else {
+                    b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
+                    e = min(__shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31), stored);
+                }
                 if (need) {
                     if (rank < take) {
-                        my_row = nr; begin = b; end = e; pos = b & ~(kGroup - 1);
-                        run = lane_const - 2u * (unsigned)(b & (kGroup - 1));   // the unit that holds `begin` starts before the row
+                        if constexpr (PLAN) {
+                            my_row = 0;
+                            out_word = __ldg(extra.plan.out + sorted_index(nr));   // needed only when the virtual row ends
+                        } else {
+                            my_row = nr;
+                        }
+                        begin = b; end = e; pos = b & ~(kGroup - 1);
+                        run = lane_const + colbase2 - 2u * (unsigned)(b & (kGroup - 1));   // the unit that holds `begin` starts before the row
                     } else {
                         my_row = -1; pos = 0; end = 0; begin = 0;
                     }
@@ -328,6 +440,52 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 }
             }
         }
+
+        // ---- first pass only: with the first matrix loads in flight, wait for the previous kernel of the
+        //      stream (if that has not happened yet) and stage x into shared memory, framed by zeros. Every
+        //      warp comes through here, also one without rows. ---------------------------------------------
+        if (first_pass) {
+            first_pass = false;
+            if (matrix_early) asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (BV > 1) {
+                __half *xs = reinterpret_cast<__half *>(smem);
+                const int n_total = (kXPadFront + cols + kXPadBack) * BV;
+#pragma unroll 1
+                for (int i = tid; i < kXPadFront * BV; i += kThreads) xs[i] = __ushort_as_half(0);
+#pragma unroll 1
+                for (int i = (kXPadFront + cols) * BV + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
+#pragma unroll
+                for (int b = 0; b < BV; ++b) {
+                    const __half *xb = x + (size_t)b * cols;
+#pragma unroll 1
+                    for (int c = tid; c < cols; c += kThreads)
+                        xs[(size_t)(kXPadFront + c) * BV + b] = b < batch ? xb[c] : __ushort_as_half(0);
+                }
+                __syncthreads();
+            } else if (XS) {
+                __half *xs = reinterpret_cast<__half *>(smem);
+                const int n_total = kXPadFront + cols + kXPadBack;
+#pragma unroll 1
+                for (int i = tid; i < kXPadFront; i += kThreads) xs[i] = __ushort_as_half(0);
+#pragma unroll 1
+                for (int i = kXPadFront + cols + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
+                if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(x);
+                    uint4 *dst = reinterpret_cast<uint4 *>(xs + kXPadFront);
+                    const int n_vec = cols >> 3;
+    #pragma unroll 1
+                for (int i = tid; i < n_vec; i += kThreads) dst[i] = __ldg(src + i);
+#pragma unroll 1
+                    for (int i = (n_vec << 3) + tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
+                } else {
+    #pragma unroll 1
+                for (int i = tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
+                }
+                __syncthreads();
+            }
+        }
+        if (done) break;
+
         // Which sub-steps hold a unit that straddles the first or the last element of a row, and how far the
         // longest row of the warp still reaches: two warp-wide reductions per iteration replace a vote per unit.
         unsigned mybits = 0u;
@@ -424,14 +582,14 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                         xe[3] = gather(add_byte<3>(ce[hs], (int)a0));
                         xo[3] = gather(add_byte<3>(co[hs], (int)a0));
                     }
-                    acc0 = fma_h<0>(acc0, vw[0], xe[0]);
-                    acc1 = fma_h<1>(acc1, vw[0], xo[0]);
-                    acc2 = fma_h<0>(acc2, vw[1], xe[1]);
-                    acc3 = fma_h<1>(acc3, vw[1], xo[1]);
-                    acc0 = fma_h<0>(acc0, vw[2], xe[2]);
-                    acc1 = fma_h<1>(acc1, vw[2], xo[2]);
-                    acc2 = fma_h<0>(acc2, vw[3], xe[3]);
-                    acc3 = fma_h<1>(acc3, vw[3], xo[3]);
+                    acc0 = fma_h<0, BF>(acc0, vw[0], xe[0]);
+                    acc1 = fma_h<1, BF>(acc1, vw[0], xo[0]);
+                    acc2 = fma_h<0, BF>(acc2, vw[1], xe[1]);
+                    acc3 = fma_h<1, BF>(acc3, vw[1], xo[1]);
+                    acc0 = fma_h<0, BF>(acc0, vw[2], xe[2]);
+                    acc1 = fma_h<1, BF>(acc1, vw[2], xo[2]);
+                    acc2 = fma_h<0, BF>(acc2, vw[3], xe[3]);
+                    acc3 = fma_h<1, BF>(acc3, vw[3], xo[3]);
                 }
             }
         }
@@ -463,43 +621,57 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         }
         __syncthreads();
         if (is_last_cta) {
-            // forward this rank's slice (read around L1: other SMs wrote it) to every other rank
+            // Forward this rank's slice (read around L1: other SMs wrote it) to every other rank; chunk c of the
+            // slice goes to all peers before chunk c + kThreads, so the stores to different peers are in flight together.
             const unsigned short *src = reinterpret_cast<const unsigned short *>(peers.y[peers.rank] + peers.row_offset);
-            const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-            for (int p = 0; p < peers.world; ++p) {
-                if (p == peers.rank) continue;
-                unsigned short *dst = reinterpret_cast<unsigned short *>(peers.y[p] + peers.row_offset);
-                if (vec && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                    const int chunks = rows >> 3;
-                    for (int c = tid; c < chunks; c += kThreads)
-                        reinterpret_cast<uint4 *>(dst)[c] = __ldcg(reinterpret_cast<const uint4 *>(src) + c);
-                    for (int i = (chunks << 3) + tid; i < rows; i += kThreads) dst[i] = __ldcg(src + i);
-                } else {
-                    for (int i = tid; i < rows; i += kThreads) dst[i] = __ldcg(src + i);
+            bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+            for (int p = 0; p < peers.world; ++p)
+                vec = vec && ((reinterpret_cast<uintptr_t>(peers.y[p] + peers.row_offset) & 15) == 0);
+            if (vec) {
+                const int chunks = rows >> 3;
+                for (int c = tid; c < chunks; c += kThreads) {
+                    const uint4 val = __ldcg(reinterpret_cast<const uint4 *>(src) + c);
+                    for (int p = 0; p < peers.world; ++p)
+                        if (p != peers.rank) reinterpret_cast<uint4 *>(peers.y[p] + peers.row_offset)[c] = val;
+                }
+                for (int i = (chunks << 3) + tid; i < rows; i += kThreads) {
+                    const unsigned short val = __ldcg(src + i);
+                    for (int p = 0; p < peers.world; ++p)
+                        if (p != peers.rank) reinterpret_cast<unsigned short *>(peers.y[p] + peers.row_offset)[i] = val;
+                }
+            } else {
+                for (int i = tid; i < rows; i += kThreads) {
+                    const unsigned short val = __ldcg(src + i);
+                    for (int p = 0; p < peers.world; ++p)
+                        if (p != peers.rank) reinterpret_cast<unsigned short *>(peers.y[p] + peers.row_offset)[i] = val;
                 }
             }
             __syncthreads();   // inside a CTA-uniform branch: all forwarding stores are issued
             if (tid == 0) {
-                __threadfence_system();   // cumulative over what the barrier ordered before it: the forwarded slice is out
+                // One system-scope fence, cumulative over what the barrier ordered before it (the forwarded slice),
+                // then the arrival counters of all ranks as plain system-scope stores behind it: a release per
+                // counter would wait for a round trip over NVLink each time.
+                __threadfence_system();
                 unsigned *mine = peers.flags[peers.rank];
                 const unsigned seq = mine[peers.world] + 1u;
                 mine[peers.world] = seq;
                 mine[peers.world + 1] = 0u;
-                for (int p = 0; p < peers.world; ++p)   // release at system scope: ordered after everything above
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + peers.rank), "r"(seq) : "memory");
+                for (int p = 0; p < peers.world; ++p)
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + peers.rank), "r"(seq) : "memory");
                 last_cta_seq = seq;
             }
             __syncthreads();
         }
-        // The CTA that finished last stays until the slices of all other ranks have arrived, so the end of
-        // this kernel means that this rank's full y is complete. Its own flags are already out, so no rank
-        // waits for a kernel that waits for it; the wait is bounded and records who was missing.
+        // Unless the caller asked for a deferred wait, the CTA that finished last stays until the slices of all
+        // other ranks have arrived, so the end of this kernel means that this rank's full y is complete. Its own
+        // counters are already out, so no rank waits for a kernel that waits for it; the wait is bounded and
+        // records who was missing.
         const unsigned seq = last_cta_seq;
-        if (seq != 0u && tid < peers.world) {
+        if (seq != 0u && !peers.deferred && tid < peers.world) {
             unsigned *mine = peers.flags[peers.rank];
             unsigned seen = 0u;
             bool arrived = false;
-            for (unsigned spin = 0; spin < (1u << 23); ++spin) {
+            for (unsigned spin = 0; spin < peers.spin_limit; ++spin) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + tid) : "memory");
                 if ((int)(seen - seq) >= 0) { arrived = true; break; }
             }
@@ -509,14 +681,15 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
 }
 
 // Waits (bounded) until every rank's arrival counter has reached this rank's own call counter, i.e.
-// until all slices of the current row-sharded product have landed in this rank's full y.
-__global__ void peer_wait_kernel(unsigned *flags, int world)
+// until all slices of the row-sharded products issued so far have landed in this rank's full y.
+__global__ void peer_wait_kernel(unsigned *flags, int world, unsigned spin_limit)
 {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int p = threadIdx.x;
     if (p >= world) return;
     const unsigned expected = flags[world];
     unsigned seen = 0;
-    for (unsigned spin = 0; spin < (1u << 23); ++spin) {
+    for (unsigned spin = 0; spin < spin_limit; ++spin) {
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + p) : "memory");
         if ((int)(seen - expected) >= 0) return;
     }
@@ -534,15 +707,18 @@ bool use_pdl()
     return on;
 }
 
-template <int L, int NPAIR, bool XS, bool PEER = false, int BV = 1>
+template <int L, int NPAIR, bool XS, bool PEER = false, int BV = 1, bool PLAN = false, bool BF = false>
 int launch(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
            const void *x, void *y, float alpha, float beta, cudaStream_t stream,
-           const DeviceInfo &dev, int ctas_per_sm, const Peers &peers = Peers{}, int batch = 1)
+           const DeviceInfo &dev, int ctas_per_sm, const Peers &peers = Peers{}, int batch = 1, const Extra &extra = Extra{})
 {
     size_t smem = XS ? (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) * BV : 0;
     if (PEER)  // staging area for a CTA's slice of y (a CTA never owns more rows than rows / #SMs + rounding)
         smem = ((smem + 15) & ~(size_t)15) + (size_t)(rows / dev.sm_count + kWarpsPerCta * 8 + 8) * sizeof(__half);
-    auto kernel = spmv_kernel<L, NPAIR, XS, PEER, BV>;
+    if (smem > (size_t)dev.max_smem_optin)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "the launch needs %lld bytes of shared memory, the device offers %d (cols=%d)",
+                    (long long)smem, dev.max_smem_optin, cols);
+    auto kernel = spmv_kernel<L, NPAIR, XS, PEER, BV, PLAN, BF>;
     if (smem > 48 * 1024) {
         // Idempotent and cheap; set on every call so that every device is covered.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -552,7 +728,8 @@ int launch(const void *values, const void *deltas, const int32_t *ri, int rows, 
     if (smem > 0) per_sm = max(1, min(per_sm, (int)((size_t)dev.max_smem_optin / (smem + 1024))));
     // Always a whole number of CTAs per SM: with fewer CTAs than that, some SMs would hold twice the rows
     // of others. Only matrices with fewer row groups than CTAs get a smaller grid (one group per CTA).
-    const long long groups = ((long long)rows * L + 31) / 32;
+    const long long work_rows = PLAN ? (long long)extra.plan.n_virtual : (long long)rows;
+    const long long groups = (work_rows * L + 31) / 32;
     long long ctas = (long long)dev.sm_count * per_sm;
     if (groups < ctas) ctas = groups < 1 ? 1 : groups;
     cudaLaunchConfig_t cfg = {};
@@ -564,40 +741,41 @@ int launch(const void *values, const void *deltas, const int32_t *ri, int rows, 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    // The scatter variant ends with a CTA that waits for other GPUs; letting the next kernel move in
-    // early only takes SM slots away from it (measured: slower), so it launches without the overlap.
-    cfg.numAttrs = (use_pdl() && !PEER) ? 1 : 0;
+    // A scatter launch that ends with a CTA waiting for other GPUs launches without the overlap: letting the
+    // next kernel move in early only takes SM slots away from it (measured: slower). With a deferred wait the
+    // kernel publishes and returns, and overlaps like any other.
+    cfg.numAttrs = (use_pdl() && (!PEER || peers.deferred)) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel,
         static_cast<const uint4 *>(values), static_cast<const unsigned *>(deltas), ri,
-        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta, peers, batch);
+        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta, peers, batch, extra);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "spmv launch: %s", cudaGetErrorString(e));
     return MACKO_OK;
 }
 
-template <int L, bool XS>
+template <int L, bool XS, bool BF>
 int launch_d(int D, const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
              const void *x, void *y, float alpha, float beta, cudaStream_t stream,
-             const DeviceInfo &dev, int ctas_per_sm)
+             const DeviceInfo &dev, int ctas_per_sm, const Extra &extra)
 {
     switch (D) {
-        case 2: return launch<L, 1, XS>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 4: return launch<L, 2, XS>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 6: return launch<L, 3, XS>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 2: return launch<L, 1, XS, false, 1, false, BF>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
+        case 4: return launch<L, 2, XS, false, 1, false, BF>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
+        case 6: return launch<L, 3, XS, false, 1, false, BF>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
         default: return fail(MACKO_ERR_INVALID_ARGUMENT, "steps_in_flight must be 2, 4 or 6 (got %d)", D);
     }
 }
 
-template <bool XS>
+template <bool XS, bool BF = false>
 int launch_l(int L, int D, const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
              const void *x, void *y, float alpha, float beta, cudaStream_t stream,
-             const DeviceInfo &dev, int ctas_per_sm)
+             const DeviceInfo &dev, int ctas_per_sm, const Extra &extra = Extra{})
 {
     switch (L) {
-        case 4: return launch_d<4, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 8: return launch_d<8, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 16: return launch_d<16, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
-        case 32: return launch_d<32, XS>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm);
+        case 4: return launch_d<4, XS, BF>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
+        case 8: return launch_d<8, XS, BF>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
+        case 16: return launch_d<16, XS, BF>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
+        case 32: return launch_d<32, XS, BF>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
         default: return fail(MACKO_ERR_INVALID_ARGUMENT, "lanes_per_row must be 4, 8, 16 or 32 (got %d)", L);
     }
 }
@@ -673,6 +851,46 @@ int check_args(const void *values, const void *deltas, const int32_t *ri, int64_
 }  // namespace
 }  // namespace macko
 
+namespace macko {
+namespace {
+
+int check_flags(uint32_t flags)
+{
+    if (flags & ~(uint32_t)MACKO_SPMV_MATRIX_IMMUTABLE)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
+    return MACKO_OK;
+}
+
+// The default launch: shape from the chooser, x in shared memory when it fits.
+template <bool BF>
+int spmv_default(const void *values, const void *deltas, const int32_t *row_indices,
+                 int64_t rows, int64_t cols, int64_t padded_count,
+                 const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream)
+{
+    int st = check_args(values, deltas, row_indices, rows, cols, padded_count, x, y);
+    if (st == MACKO_OK) st = check_flags(flags);
+    if (st != MACKO_OK) return st;
+    if (rows == 0) return MACKO_OK;
+    const DeviceInfo *dev = nullptr;
+    st = current_device_info(&dev);
+    if (st != MACKO_OK) return st;
+
+    const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
+    const int ctas = smem * 2 + 2048 <= (size_t)dev->max_smem_optin ? 2 : 1;
+    const Shape shape = choose_shape(rows, cols, padded_count, dev->sm_count * ctas * kWarpsPerCta);
+    const int L = shape.L, D = shape.D;
+    const bool xs = smem <= (size_t)dev->max_smem_optin;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    Extra extra = {};
+    extra.flags = flags;
+    if (xs)
+        return launch_l<true, BF>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
+    return launch_l<false, BF>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
+}
+
+}  // namespace
+}  // namespace macko
+
 extern "C" {
 
 int macko_spmv_fp16_tuned(const void *values, const void *deltas, const int32_t *row_indices,
@@ -688,6 +906,7 @@ int macko_spmv_fp16_tuned(const void *values, const void *deltas, const int32_t 
     const DeviceInfo *dev = nullptr;
     st = current_device_info(&dev);
     if (st != MACKO_OK) return st;
+    if (cols == 0) x_in_shared = 1;   // nothing to gather: the zero frame in shared memory serves every (malformed) element
     const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
     if (x_in_shared && smem > (size_t)dev->max_smem_optin)
         return fail(MACKO_ERR_INVALID_ARGUMENT, "x does not fit shared memory (cols=%lld)", (long long)cols);
@@ -703,23 +922,62 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
                     int64_t rows, int64_t cols, int64_t padded_count,
                     const void *x, void *y, float alpha, float beta, void *stream)
 {
+    return macko::spmv_default<false>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, 0u, stream);
+}
+
+int macko_spmv_fp16_ex(const void *values, const void *deltas, const int32_t *row_indices,
+                       int64_t rows, int64_t cols, int64_t padded_count,
+                       const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream)
+{
+    return macko::spmv_default<false>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, flags, stream);
+}
+
+int macko_spmv_bf16(const void *values, const void *deltas, const int32_t *row_indices,
+                    int64_t rows, int64_t cols, int64_t padded_count,
+                    const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream)
+{
+    return macko::spmv_default<true>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, flags, stream);
+}
+
+int macko_spmv_fp16_planned(const void *values, const void *deltas, const int32_t *row_indices,
+                            int64_t rows, int64_t cols, int64_t padded_count,
+                            const void *plan, const macko_spmv_plan_info *info,
+                            const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream)
+{
     using namespace macko;
     int st = check_args(values, deltas, row_indices, rows, cols, padded_count, x, y);
+    if (st == MACKO_OK) st = check_flags(flags);
     if (st != MACKO_OK) return st;
+    if (!plan || !info) return fail(MACKO_ERR_INVALID_ARGUMENT, "null plan or plan info");
+    if (!aligned(plan, 16)) return fail(MACKO_ERR_MISALIGNED, "plan must be 16-byte aligned");
+    if (info->rows != rows || info->padded_count != padded_count || info->virtual_rows < rows ||
+        info->segment_elements < 256 || info->segment_elements > kPlanMaxSegment || info->segment_elements % 256 != 0)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "the plan info does not describe this matrix (rows %lld/%lld, P %lld/%lld, %d virtual rows)",
+                    (long long)info->rows, (long long)rows, (long long)info->padded_count, (long long)padded_count, info->virtual_rows);
+    const PlanLayout lay = plan_layout(rows, padded_count, info->segment_elements);
+    if (info->plan_bytes != lay.total || (long long)info->virtual_rows > lay.v_max)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "the plan info is inconsistent (bytes %lld, expected %lld)",
+                    (long long)info->plan_bytes, (long long)lay.total);
     if (rows == 0) return MACKO_OK;
     const DeviceInfo *dev = nullptr;
     st = current_device_info(&dev);
     if (st != MACKO_OK) return st;
-
     const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
-    const int ctas = smem * 2 + 2048 <= (size_t)dev->max_smem_optin ? 2 : 1;
-    const Shape shape = choose_shape(rows, cols, padded_count, dev->sm_count * ctas * kWarpsPerCta);
-    const int L = shape.L, D = shape.D;
-    const bool xs = smem <= (size_t)dev->max_smem_optin;
+    if (smem > (size_t)dev->max_smem_optin)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "cols=%lld does not fit shared memory in the planned launch", (long long)cols);
+    char *base = const_cast<char *>(static_cast<const char *>(plan));
+    Extra extra = {};
+    extra.flags = flags;
+    extra.plan.desc = reinterpret_cast<const uint2 *>(base + lay.desc);
+    extra.plan.out = reinterpret_cast<const unsigned *>(base + lay.out);
+    extra.plan.vrow = reinterpret_cast<const unsigned *>(base + lay.vrow);
+    extra.plan.partial = reinterpret_cast<float *>(base + lay.partial);
+    extra.plan.seg_first = reinterpret_cast<const int *>(base + lay.seg_first);
+    extra.plan.arrived = reinterpret_cast<unsigned *>(base + lay.arrived);
+    extra.plan.n_virtual = info->virtual_rows;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (xs)
-        return launch_l<true>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
-    return launch_l<false>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0);
+    return launch<8, 3, true, false, 1, true>(values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y,
+                                              alpha, beta, s, *dev, 0, Peers{}, 1, extra);
 }
 
 int macko_spmv_shape(int64_t rows, int64_t cols, int64_t padded_count, int sm_count,
@@ -776,16 +1034,18 @@ int macko_spmm_fp16(const void *values, const void *deltas, const int32_t *row_i
     return MACKO_OK;
 }
 
-int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_t *row_indices,
-                            int64_t rows, int64_t cols, int64_t padded_count, const void *x,
-                            void *const *peer_y, int64_t row_offset, uint32_t *const *peer_flags,
-                            int rank, int world, void *stream)
+int macko_spmv_fp16_scatter_ex(const void *values, const void *deltas, const int32_t *row_indices,
+                               int64_t rows, int64_t cols, int64_t padded_count, const void *x,
+                               void *const *peer_y, int64_t row_offset, uint32_t *const *peer_flags,
+                               int rank, int world, uint32_t flags, uint32_t spin_limit, void *stream)
 {
     using namespace macko;
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
         return fail(MACKO_ERR_INVALID_ARGUMENT, "rank %d / world %d outside 1..%d", rank, world, kMaxPeers);
     if (!peer_y || !peer_flags || row_offset < 0)
         return fail(MACKO_ERR_INVALID_ARGUMENT, "null peer tables or negative row offset");
+    if (flags & ~(uint32_t)(MACKO_SPMV_MATRIX_IMMUTABLE | MACKO_SCATTER_DEFERRED_WAIT))
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
     Peers peers = {};
     for (int p = 0; p < world; ++p) {
         if (!peer_y[p] || !peer_flags[p]) return fail(MACKO_ERR_INVALID_ARGUMENT, "null pointer for rank %d", p);
@@ -797,22 +1057,29 @@ int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_
     peers.row_offset = row_offset;
     peers.world = world;
     peers.rank = rank;
+    peers.spin_limit = spin_limit == 0 ? kDefaultSpinLimit : spin_limit;
+    peers.deferred = (flags & MACKO_SCATTER_DEFERRED_WAIT) ? 1 : 0;
     int st = check_args(values, deltas, row_indices, rows, cols, padded_count, x, peer_y[rank]);
     if (st != MACKO_OK) return st;
     const DeviceInfo *dev = nullptr;
     st = current_device_info(&dev);
     if (st != MACKO_OK) return st;
-    const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half);
+    // x and the CTA's slice of y share the CTA's shared memory (launch() refuses what does not fit)
+    const size_t smem = (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) +
+                        (size_t)(rows / dev->sm_count + kWarpsPerCta * 8 + 16) * sizeof(__half);
     if (smem > (size_t)dev->max_smem_optin)
-        return fail(MACKO_ERR_INVALID_ARGUMENT, "cols=%lld does not fit shared memory in the scatter variant", (long long)cols);
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "cols=%lld (plus the y staging of %lld rows) does not fit shared memory in the scatter variant",
+                    (long long)cols, (long long)rows);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // rows == 0 still has to signal: launch the kernel with an empty range (one CTA)
     const int ctas = smem * 2 + 4096 <= (size_t)dev->max_smem_optin ? 2 : 1;
     Shape shape = choose_shape(rows, cols, padded_count, dev->sm_count * ctas * kWarpsPerCta);
     if (shape.L < 8) shape.L = 8;   // the scatter variant is built for 8, 16 and 32 lanes per row
     const int r = (int)rows, c = (int)cols;
+    Extra extra = {};
+    extra.flags = flags & MACKO_SPMV_MATRIX_IMMUTABLE;
 #define MACKO_SCATTER(LL, NP) \
-    launch<LL, NP, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers)
+    launch<LL, NP, true, true>(values, deltas, row_indices, r, c, padded_count, x, nullptr, 1.f, 0.f, s, *dev, 0, peers, 1, extra)
     switch (shape.L * 10 + shape.D) {
         case 82: return MACKO_SCATTER(8, 1);
         case 84: return MACKO_SCATTER(8, 2);
@@ -827,14 +1094,30 @@ int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_
 #undef MACKO_SCATTER
 }
 
-int macko_peer_wait(uint32_t *local_flags, int world, void *stream)
+int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_t *row_indices,
+                            int64_t rows, int64_t cols, int64_t padded_count, const void *x,
+                            void *const *peer_y, int64_t row_offset, uint32_t *const *peer_flags,
+                            int rank, int world, void *stream)
+{
+    return macko_spmv_fp16_scatter_ex(values, deltas, row_indices, rows, cols, padded_count, x, peer_y, row_offset,
+                                      peer_flags, rank, world, 0u, 0u, stream);
+}
+
+int macko_peer_wait_limited(uint32_t *local_flags, int world, uint32_t spin_limit, void *stream)
 {
     using namespace macko;
     if (!local_flags || world < 1 || world > kMaxPeers)
         return fail(MACKO_ERR_INVALID_ARGUMENT, "null flags or world %d outside 1..%d", world, kMaxPeers);
-    peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(local_flags, world);
+    if (!aligned(local_flags, 4)) return fail(MACKO_ERR_MISALIGNED, "flags must be 4-byte aligned");
+    peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(local_flags, world,
+                                                                        spin_limit == 0 ? kDefaultSpinLimit : spin_limit);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "peer wait launch: %s", cudaGetErrorString(e));
     return MACKO_OK;
+}
+
+int macko_peer_wait(uint32_t *local_flags, int world, void *stream)
+{
+    return macko_peer_wait_limited(local_flags, world, 0u, stream);
 }
 }

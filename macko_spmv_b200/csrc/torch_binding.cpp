@@ -26,7 +26,8 @@ void check_status(int status, const char *what)
 void check_compressed(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
                       int64_t rows, int64_t cols)
 {
-    TORCH_CHECK(values.dtype() == at::kHalf, "M must be torch.half");
+    // fp16 is the reference's type; bfloat16 runs the same layout through the bf16 kernel
+    TORCH_CHECK(values.dtype() == at::kHalf || values.dtype() == at::kBFloat16, "M must be torch.half");
     TORCH_CHECK(deltas.dtype() == at::kByte, "M_deltas must be torch.uint8");
     TORCH_CHECK(ri.dtype() == at::kInt, "M_row_indices must be torch.int32");
     TORCH_CHECK(values.is_cuda() && deltas.is_cuda() && ri.is_cuda(), "compressed buffers must be CUDA tensors");
@@ -40,12 +41,12 @@ void check_compressed(const at::Tensor &values, const at::Tensor &deltas, const 
                 "values / deltas sizes are not a MACKO pair");
 }
 
-// y[..., rows] for V[..., cols]; one SpMV per leading index.
-at::Tensor multiply_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
-                         int64_t rows, int64_t cols, const at::Tensor &V)
+// y[rows] for V[cols]. `flags`: MACKO_SPMV_MATRIX_IMMUTABLE or 0.
+at::Tensor multiply_flags(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
+                          int64_t rows, int64_t cols, const at::Tensor &V, uint32_t flags)
 {
     check_compressed(values, deltas, ri, rows, cols);
-    TORCH_CHECK(V.dtype() == at::kHalf, "V must be torch.half");
+    TORCH_CHECK(V.dtype() == values.dtype(), "V must be torch.half");
     TORCH_CHECK(V.is_cuda() && V.device() == values.device(), "V must be on the device of M");
     TORCH_CHECK(V.is_contiguous(), "V must be contiguous");
     TORCH_CHECK(V.dim() == 1 && V.size(0) == cols, "V must have shape [M_cols]");
@@ -53,9 +54,80 @@ at::Tensor multiply_cuda(const at::Tensor &values, const at::Tensor &deltas, con
     const c10::cuda::CUDAGuard guard(values.device());
     at::Tensor y = at::empty({rows}, values.options());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
-    check_status(macko_spmv_fp16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
-                                 values.numel(), V.data_ptr(), y.data_ptr(), 1.0f, 0.0f, stream),
-                 "macko_spmv_fp16");
+    if (values.dtype() == at::kBFloat16)
+        check_status(macko_spmv_bf16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                     values.numel(), V.data_ptr(), y.data_ptr(), 1.0f, 0.0f, flags, stream),
+                     "macko_spmv_bf16");
+    else
+        check_status(macko_spmv_fp16_ex(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                        values.numel(), V.data_ptr(), y.data_ptr(), 1.0f, 0.0f, flags, stream),
+                     "macko_spmv_fp16");
+    return y;
+}
+
+at::Tensor multiply_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
+                         int64_t rows, int64_t cols, const at::Tensor &V)
+{
+    return multiply_flags(values, deltas, ri, rows, cols, V, 0u);
+}
+
+// The same product for a matrix the caller has declared immutable (weights): the kernel may fetch matrix
+// data before the previous kernel of the stream has finished.
+at::Tensor multiply_frozen_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
+                                int64_t rows, int64_t cols, const at::Tensor &V)
+{
+    return multiply_flags(values, deltas, ri, rows, cols, V, MACKO_SPMV_MATRIX_IMMUTABLE);
+}
+
+// Plan of a compressed matrix: (plan buffer on the device, int64[8] on the host =
+// plan_bytes, rows, padded_count, virtual_rows, segment_elements, longest_row, split_rows, recommended).
+std::tuple<at::Tensor, at::Tensor> plan_build_cuda(const at::Tensor &deltas, const at::Tensor &ri, int64_t rows,
+                                                   int64_t cols, int64_t padded, int64_t segment_elements)
+{
+    TORCH_CHECK(deltas.is_cuda() && ri.is_cuda() && deltas.device() == ri.device(), "compressed buffers must be CUDA tensors");
+    TORCH_CHECK(deltas.dtype() == at::kByte && ri.dtype() == at::kInt, "M_deltas must be uint8 and M_row_indices int32");
+    TORCH_CHECK(deltas.is_contiguous() && ri.is_contiguous(), "compressed buffers must be contiguous");
+    TORCH_CHECK(ri.numel() == rows + 1 && deltas.numel() * 2 == padded, "sizes are not those of a MACKO matrix");
+    const int64_t bytes = macko_spmv_plan_bytes(rows, cols, padded, (int32_t)segment_elements);
+    TORCH_CHECK(bytes >= 0, "macko_spmv_plan_bytes: ", macko_last_error());
+    const c10::cuda::CUDAGuard guard(deltas.device());
+    at::Tensor plan = at::empty({bytes}, deltas.options());
+    macko_spmv_plan_info info;
+    cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
+    check_status(macko_spmv_plan(deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols, padded, (int32_t)segment_elements,
+                                 plan.data_ptr(), bytes, &info, stream),
+                 "macko_spmv_plan");
+    at::Tensor meta = at::empty({8}, at::TensorOptions().dtype(at::kLong).device(at::kCPU));
+    int64_t *m = meta.data_ptr<int64_t>();
+    m[0] = info.plan_bytes; m[1] = info.rows; m[2] = info.padded_count; m[3] = info.virtual_rows;
+    m[4] = info.segment_elements; m[5] = info.longest_row; m[6] = info.split_rows; m[7] = info.recommended;
+    return std::make_tuple(plan, meta);
+}
+
+at::Tensor multiply_planned_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
+                                 int64_t rows, int64_t cols, const at::Tensor &plan, int64_t virtual_rows,
+                                 int64_t segment_elements, const at::Tensor &V, bool frozen)
+{
+    check_compressed(values, deltas, ri, rows, cols);
+    TORCH_CHECK(values.dtype() == at::kHalf && V.dtype() == at::kHalf, "the planned product is built for torch.half");
+    TORCH_CHECK(V.is_cuda() && V.device() == values.device() && plan.is_cuda() && plan.device() == values.device(),
+                "V and the plan must be on the device of M");
+    TORCH_CHECK(V.is_contiguous() && plan.is_contiguous(), "V and the plan must be contiguous");
+    TORCH_CHECK(V.dim() == 1 && V.size(0) == cols, "V must have shape [M_cols]");
+    macko_spmv_plan_info info = {};
+    info.plan_bytes = macko_spmv_plan_bytes(rows, cols, values.numel(), (int32_t)segment_elements);
+    TORCH_CHECK(info.plan_bytes >= 0 && plan.numel() * plan.element_size() >= info.plan_bytes, "plan buffer too small for this matrix");
+    info.rows = rows;
+    info.padded_count = values.numel();
+    info.virtual_rows = (int32_t)virtual_rows;
+    info.segment_elements = (int32_t)segment_elements;
+    const c10::cuda::CUDAGuard guard(values.device());
+    at::Tensor y = at::empty({rows}, values.options());
+    cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
+    check_status(macko_spmv_fp16_planned(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                         values.numel(), plan.data_ptr(), &info, V.data_ptr(), y.data_ptr(), 1.0f, 0.0f,
+                                         frozen ? MACKO_SPMV_MATRIX_IMMUTABLE : 0u, stream),
+                 "macko_spmv_fp16_planned");
     return y;
 }
 
@@ -64,16 +136,21 @@ void multiply_out_cuda(const at::Tensor &values, const at::Tensor &deltas, const
                        int64_t rows, int64_t cols, const at::Tensor &V, at::Tensor y, double alpha, double beta)
 {
     check_compressed(values, deltas, ri, rows, cols);
-    TORCH_CHECK(V.dtype() == at::kHalf && y.dtype() == at::kHalf, "V and y must be torch.half");
+    TORCH_CHECK(V.dtype() == values.dtype() && y.dtype() == values.dtype(), "V and y must be torch.half");
     TORCH_CHECK(V.is_cuda() && V.device() == values.device() && y.device() == values.device(),
                 "V and y must be on the device of M");
     TORCH_CHECK(V.is_contiguous() && y.is_contiguous(), "V and y must be contiguous");
     TORCH_CHECK(V.dim() == 1 && V.size(0) == cols && y.dim() == 1 && y.size(0) == rows, "bad vector shapes");
     const c10::cuda::CUDAGuard guard(values.device());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
-    check_status(macko_spmv_fp16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
-                                 values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, stream),
-                 "macko_spmv_fp16");
+    if (values.dtype() == at::kBFloat16)
+        check_status(macko_spmv_bf16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                     values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, 0u, stream),
+                     "macko_spmv_bf16");
+    else
+        check_status(macko_spmv_fp16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                     values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, stream),
+                     "macko_spmv_fp16");
 }
 
 // Y[batch, rows] for V[batch, cols]: up to 8 vectors per pass over the compressed matrix.
@@ -81,7 +158,7 @@ at::Tensor multiply_batched_cuda(const at::Tensor &values, const at::Tensor &del
                                  int64_t rows, int64_t cols, const at::Tensor &V)
 {
     check_compressed(values, deltas, ri, rows, cols);
-    TORCH_CHECK(V.dtype() == at::kHalf, "V must be torch.half");
+    TORCH_CHECK(values.dtype() == at::kHalf && V.dtype() == at::kHalf, "M and V must be torch.half");
     TORCH_CHECK(V.is_cuda() && V.device() == values.device(), "V must be on the device of M");
     TORCH_CHECK(V.is_contiguous(), "V must be contiguous");
     TORCH_CHECK(V.dim() == 2 && V.size(1) == cols, "V must have shape [batch, M_cols]");
@@ -110,7 +187,7 @@ at::Tensor decompress_cuda(const at::Tensor &values, const at::Tensor &deltas, c
 std::tuple<at::Tensor, at::Tensor, at::Tensor> compress_cuda(const at::Tensor &M)
 {
     TORCH_CHECK(M.is_cuda(), "M must be a CUDA tensor");
-    TORCH_CHECK(M.dtype() == at::kHalf, "M must be torch.half");
+    TORCH_CHECK(M.dtype() == at::kHalf || M.dtype() == at::kBFloat16, "M must be torch.half");
     TORCH_CHECK(M.dim() == 2, "M must be a matrix");
     TORCH_CHECK(M.is_contiguous(), "M must be contiguous");
     const int64_t rows = M.size(0), cols = M.size(1);
@@ -126,9 +203,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> compress_cuda(const at::Tensor &M
     at::Tensor deltas = at::empty({padded / 2}, M.options().dtype(at::kByte));
     const int64_t ws_bytes = macko_compress_workspace_bytes(padded);
     at::Tensor ws = at::empty({ws_bytes}, M.options().dtype(at::kByte));
-    check_status(macko_compress_emit(M.data_ptr(), rows, cols, ri.data_ptr<int32_t>(), padded,
-                                     values.data_ptr(), deltas.data_ptr(), ws.data_ptr(), ws_bytes, stream),
-                 "macko_compress_emit");
+    if (M.dtype() == at::kBFloat16)
+        check_status(macko_compress_emit_bf16(M.data_ptr(), rows, cols, ri.data_ptr<int32_t>(), padded,
+                                              values.data_ptr(), deltas.data_ptr(), ws.data_ptr(), ws_bytes, stream),
+                     "macko_compress_emit_bf16");
+    else
+        check_status(macko_compress_emit(M.data_ptr(), rows, cols, ri.data_ptr<int32_t>(), padded,
+                                         values.data_ptr(), deltas.data_ptr(), ws.data_ptr(), ws_bytes, stream),
+                     "macko_compress_emit");
     return std::make_tuple(values, deltas, ri);
 }
 
@@ -142,6 +224,10 @@ TORCH_LIBRARY(macko_spmv, m)
     m.def("compress_dense(Tensor M) -> (Tensor, Tensor, Tensor)");
     m.def("multiply_batched(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor V) -> Tensor");
     m.def("decompress(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols) -> Tensor");
+    m.def("multiply_frozen(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor V) -> Tensor");
+    m.def("plan_build(Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, int padded_count, int segment_elements) -> (Tensor, Tensor)");
+    m.def("multiply_planned(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor plan, "
+          "int virtual_rows, int segment_elements, Tensor V, bool frozen) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
@@ -151,4 +237,7 @@ TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
     m.impl("compress_dense", &compress_cuda);
     m.impl("multiply_batched", &multiply_batched_cuda);
     m.impl("decompress", &decompress_cuda);
+    m.impl("multiply_frozen", &multiply_frozen_cuda);
+    m.impl("plan_build", &plan_build_cuda);
+    m.impl("multiply_planned", &multiply_planned_cuda);
 }

@@ -31,6 +31,17 @@ class MackoLinear(nn.Module):
         self.register_buffer("c_1", deltas)
         self.register_buffer("c_2", row_indices)
         self.bias = nn.Parameter(bias, requires_grad=False) if bias is not None else None
+        self._frozen = None   # FrozenMatrix after freeze(): immutable weights, optional launch plan
+
+    def freeze(self, plan="auto") -> "MackoLinear":
+        """Declare the weight buffers final (call after loading / moving the module, before serving): the
+        single-vector product may then read them ahead of stream order, and matrices with very uneven rows
+        get a launch plan (see `macko_spmv_b200.freeze`). Writing c_0 / c_1 / c_2 afterwards (load_state_dict,
+        .to(...)) requires another freeze()."""
+        from . import freeze
+
+        self._frozen = freeze(self.compressed, plan=plan)
+        return self
 
     @classmethod
     def from_linear(cls, linear: nn.Linear) -> "MackoLinear":
@@ -66,7 +77,10 @@ class MackoLinear(nn.Module):
         flat = x.reshape(-1, self.in_features)
         comp = self.compressed
         if flat.shape[0] == 1:
-            y = multiply(comp, flat[0].contiguous()).unsqueeze(0)
+            fz = self._frozen
+            if fz is not None and fz[0].data_ptr() != self.c_0.data_ptr():
+                fz = self._frozen = None   # the buffers were replaced since freeze(): back to the safe path
+            y = multiply(fz if fz is not None else comp, flat[0].contiguous()).unsqueeze(0)
         else:
             y = multiply_batched(comp, flat.contiguous())
         if self.bias is not None:
@@ -139,11 +153,13 @@ def compressed_prefixes(state_dict) -> list[str]:
     return sorted({k[: -len(".c_0")] for k in state_dict if k.endswith(".c_0")})
 
 
-def replace_linears(model: nn.Module, state_dict, device="cuda") -> nn.Module:
+def replace_linears(model: nn.Module, state_dict, device="cuda", freeze: bool = False) -> nn.Module:
     """Swap the modules named by the compressed entries of `state_dict` for `MackoLinear` layers
-    (what `fix()` does in python_scripts/util_run_pruned_llm.py:123-133)."""
+    (what `fix()` does in python_scripts/util_run_pruned_llm.py:123-133). `freeze=True` also declares the
+    loaded weights final (`MackoLinear.freeze`)."""
     for prefix in compressed_prefixes(state_dict):
         parent_path, _, leaf = prefix.rpartition(".")
         parent = model.get_submodule(parent_path) if parent_path else model
-        setattr(parent, leaf, MackoLinear.from_state_dict_entry(state_dict, prefix, device))
+        layer = MackoLinear.from_state_dict_entry(state_dict, prefix, device)
+        setattr(parent, leaf, layer.freeze() if freeze else layer)
     return model

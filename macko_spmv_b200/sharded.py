@@ -120,16 +120,28 @@ def multiply_sharded(shard: RowShard, x: torch.Tensor, out: torch.Tensor | None 
 class PeerGather:
     """Row-sharded SpMV whose kernel stores y straight into every rank's full y over NVLink.
 
-    Replaces `multiply_sharded`'s NCCL all-gather by the fused epilogue of
-    `macko_spmv_fp16_scatter`: no collective call and no extra kernel (the last CTA of the grid waits
-    for the other ranks' flags before the kernel ends).
-    The full-y buffers and the flag words live in torch symmetric memory (peer-mapped on every rank).
-    Two y slots are used alternately, so the result of a call stays valid until the call after next.
+    Replaces `multiply_sharded`'s NCCL all-gather by the fused epilogue of `macko_spmv_fp16_scatter_ex`:
+    no collective call. The full-y buffers and the flag words live in torch symmetric memory (peer-mapped on
+    every rank; plain peer stores and flags, no NVLink multicast: binding to a multicast object is switched
+    off before the first allocation unless the environment already says otherwise).
+
+    Two ways to use it:
+
+    * `multiply(shard, x)`: the kernel ends only when the slices of all ranks have landed (its last CTA
+      waits, bounded). Two y slots alternate, so a result stays valid until the call after next.
+    * `begin_step()`, then any number of `multiply_deferred(shard, x)`, then `wait()`: every product
+      publishes its slice and returns at once (it overlaps with the next product like an ordinary kernel);
+      each gets its own region of the step's half of the buffer, and one bounded wait kernel at the end
+      makes all of them complete. The two halves alternate from step to step: a rank that is already in
+      step s + 1 writes into the half nobody reads any more, because it passed `wait()` of step s only
+      after every rank had delivered step s, i.e. had already consumed step s - 1 in stream order.
     """
 
-    def __init__(self, max_rows: int, device, group=None):
+    def __init__(self, max_rows: int, device, group=None, step_rows: int = 0):
         import ctypes
+        import os
 
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import cabi
@@ -137,6 +149,7 @@ class PeerGather:
         self._ctypes = ctypes
         self.lib = cabi.load()
         self.check = cabi.check
+        self._cabi = cabi
         group = group if group is not None else dist.group.WORLD
         self.group = group
         self.world = dist.get_world_size(group)
@@ -144,35 +157,79 @@ class PeerGather:
         if self.world > 8:
             raise ValueError("PeerGather supports at most 8 ranks (one NVLink domain)")
         self.max_rows = int(max_rows)
-        self.buf = symm_mem.empty((2, self.max_rows), dtype=torch.float16, device=device)
+        # rows of one deferred step (sum over its products, each rounded up to 8), at least one product
+        self.step_rows = max(int(step_rows), (self.max_rows + 7) // 8 * 8)
+        self.buf = symm_mem.empty((2, self.step_rows), dtype=torch.float16, device=device)
         self.handle = symm_mem.rendezvous(self.buf, group)
         pad = self.handle.get_signal_pad(self.rank)
         pad.zero_()
         torch.cuda.synchronize(device)
         dist.barrier(group)
-        ptr_array = ctypes.c_void_p * self.world
-        base = [int(p) for p in self.handle.buffer_ptrs]
-        self._y_tables = [ptr_array(*[b + slot * self.max_rows * 2 for b in base]) for slot in (0, 1)]
+        self._ptr_array = ctypes.c_void_p * self.world
+        self._base = [int(p) for p in self.handle.buffer_ptrs]
+        self._tables = {}
         # the flag words sit 1 KiB into each rank's signal pad, clear of the slots torch's own barriers use
-        self._flag_table = ptr_array(*[int(p) + 1024 for p in self.handle.signal_pad_ptrs])
+        self._flag_table = self._ptr_array(*[int(p) + 1024 for p in self.handle.signal_pad_ptrs])
         self._local_flags = int(self.handle.signal_pad_ptrs[self.rank]) + 1024
         self._slot = 0
+        self._half = 1
+        self._cursor = 0
+        self.spin_limit = 0   # 0 = library default (2^23 polls)
+
+    def _table(self, half: int, offset: int):
+        key = (half, offset)
+        t = self._tables.get(key)
+        if t is None:
+            t = self._ptr_array(*[b + (half * self.step_rows + offset) * 2 for b in self._base])
+            self._tables[key] = t
+        return t
+
+    def _launch(self, shard: RowShard, x: torch.Tensor, table, flags: int):
+        comp = shard.compressed
+        stream = torch.cuda.current_stream().cuda_stream
+        self.check(self.lib, self.lib.macko_spmv_fp16_scatter_ex(
+            comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
+            x.data_ptr(), table, shard.row_lo, self._flag_table, self.rank, self.world, flags, self.spin_limit, stream))
 
     def multiply(self, shard: RowShard, x: torch.Tensor) -> torch.Tensor:
         """Full y (a view of the current slot, length shard.total_rows) after all ranks delivered."""
         if shard.total_rows > self.max_rows:
             raise ValueError(f"matrix has {shard.total_rows} rows, the exchange buffers hold {self.max_rows}")
-        comp = shard.compressed
-        stream = torch.cuda.current_stream().cuda_stream
         slot = self._slot
         self._slot ^= 1
-        self.check(self.lib, self.lib.macko_spmv_fp16_scatter(
-            comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
-            x.data_ptr(), self._y_tables[slot], shard.row_lo, self._flag_table, self.rank, self.world, stream))
+        self._launch(shard, x, self._table(slot, 0), 0)
         # the kernel itself returns only after the slices of all ranks have landed (its last CTA waits)
         return self.buf[slot, : shard.total_rows]
+
+    def begin_step(self) -> None:
+        """Start a new deferred step: switch to the other half of the buffer."""
+        self._half ^= 1
+        self._cursor = 0
+
+    def multiply_deferred(self, shard: RowShard, x: torch.Tensor, immutable: bool = False) -> torch.Tensor:
+        """Enqueue the product; the returned view of the step's buffer is complete only after `wait()`."""
+        rows8 = (shard.total_rows + 7) // 8 * 8
+        if self._cursor + rows8 > self.step_rows:
+            raise ValueError(f"the step's products need more than the {self.step_rows} rows the buffers hold")
+        off = self._cursor
+        self._cursor += rows8
+        flags = self._cabi.SCATTER_DEFERRED_WAIT | (self._cabi.SPMV_MATRIX_IMMUTABLE if immutable else 0)
+        self._launch(shard, x, self._table(self._half, off), flags)
+        return self.buf[self._half, off : off + shard.total_rows]
+
+    def wait(self) -> None:
+        """Enqueue the bounded wait for the slices of all ranks of every product issued so far."""
+        stream = torch.cuda.current_stream().cuda_stream
+        self.check(self.lib, self.lib.macko_peer_wait_limited(self._local_flags, self.world, self.spin_limit, stream))
 
     def error_flag(self) -> int:
         """0, or 1 + the rank whose slice never arrived in some earlier wait (reads device memory)."""
         pad = self.handle.get_signal_pad(self.rank).view(torch.int32)
         return int(pad[256 + self.world + 2].item())
+
+    def close(self) -> None:
+        """Drop the symmetric buffers (after a device synchronisation): call before the process group is torn down."""
+        torch.cuda.synchronize()
+        self._tables.clear()
+        self.handle = None
+        self.buf = None

@@ -68,6 +68,11 @@ def skewed_matrix(rows: int, cols: int, seed: int, device="cpu", mean_density: f
     rho[perm[:n5]] = 1.0
     rho[perm[n5 : 2 * n5]] = 0.0
 
+    # The row densities above are drawn on the CPU (small); the run / gap lengths and the values, which are
+    # rows x cols sized, are drawn on `device` with that device's generator.
+    dev = torch.device(device)
+    gd = _gen(seed + 1, dev)
+    rho = rho.to(dev)
     p_run = 0.3
     mean_run = 1.0 / p_run
     # Alternating run / gap lengths, drawn for all rows at once: enough segments to cover
@@ -75,27 +80,32 @@ def skewed_matrix(rows: int, cols: int, seed: int, device="cpu", mean_density: f
     rho_c = rho.clamp(min=1e-4)
     mean_gap = (mean_run * (1.0 - rho_c) / rho_c).clamp(min=1e-3)
     n_seg = int(min(cols, max(64, 4 * cols / (mean_run + float(mean_gap.median())))))
-    u_run = torch.rand(rows, n_seg, generator=g).clamp_(min=1e-12)
-    u_gap = torch.rand(rows, n_seg, generator=g).clamp_(min=1e-12)
-    runs = torch.floor(torch.log(u_run) / math.log(1.0 - p_run)).to(torch.int64) + 1
+    u_run = torch.rand(rows, n_seg, generator=gd, device=dev).clamp_(min=1e-12)
+    runs = torch.floor(torch.log(u_run) / math.log(1.0 - p_run)).to(torch.int32) + 1
+    del u_run
+    u_gap = torch.rand(rows, n_seg, generator=gd, device=dev).clamp_(min=1e-12)
     p_gap = (1.0 / (mean_gap + 1.0)).unsqueeze(1)  # support >= 0, mean = mean_gap
-    gaps = torch.floor(torch.log(u_gap) / torch.log1p(-p_gap.clamp(max=1 - 1e-9))).to(torch.int64)
+    gaps = torch.floor(torch.log(u_gap) / torch.log1p(-p_gap.clamp(max=1 - 1e-9))).clamp_(max=cols).to(torch.int32)
+    del u_gap
     seg = torch.stack([gaps, runs], dim=2).reshape(rows, 2 * n_seg)
-    edges = torch.cumsum(seg, dim=1).clamp_(max=cols)
+    del gaps, runs
+    edges = torch.cumsum(seg, dim=1, dtype=torch.int64).clamp_(max=cols)
+    del seg
     # +1 at run starts, -1 at run ends, prefix-sum to a mask
-    marks = torch.zeros(rows, cols + 1, dtype=torch.int32)
+    marks = torch.zeros(rows, cols + 1, dtype=torch.int32, device=dev)
     starts = edges[:, 0::2]
     ends = edges[:, 1::2]
     marks.scatter_add_(1, starts, torch.ones_like(starts, dtype=torch.int32))
     marks.scatter_add_(1, ends, -torch.ones_like(ends, dtype=torch.int32))
+    del edges, starts, ends
     mask = torch.cumsum(marks[:, :cols], dim=1) > 0
+    del marks
     # rows whose segments ran out before the row end stay sparse at the tail; fine for a stress test
     mask[rho >= 1.0] = True
     mask[rho <= 0.0] = False
-    w = torch.randn(rows, cols, generator=g, dtype=torch.float32).to(torch.float16)
+    w = torch.randn(rows, cols, generator=gd, device=dev, dtype=torch.float32).to(torch.float16)
     w[w == 0] = 1.0
-    m = (w * mask).to(device)
-    return m
+    return w * mask
 
 
 def dense_vector(cols: int, seed: int, device="cpu"):

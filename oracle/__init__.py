@@ -27,14 +27,25 @@ _f64p = ctypes.POINTER(ctypes.c_double)
 _i64 = ctypes.c_int64
 
 
+def _make_env() -> dict:
+    """Environment for make: the reference checkout comes from MACKO_REFERENCE_DIR, else from a directory
+    named `reference` beside this repository, if there is one."""
+    env = dict(os.environ)
+    if not env.get("MACKO_REFERENCE_DIR"):
+        cand = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+        if os.path.isdir(cand):
+            env["MACKO_REFERENCE_DIR"] = cand
+    return env
+
+
 def build(force: bool = False) -> None:
     """Compile the oracle (and the reference compressor when its sources exist)."""
     if force or not os.path.exists(_LIB_PATH) or (
         os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "macko_oracle.c"))
     ):
-        subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True, env=_make_env())
     elif not os.path.exists(_REF_PATH) or not os.path.exists(_REF_KERNEL_PATH):
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True, env=_make_env())
 
 
 _lib = None
@@ -51,6 +62,8 @@ def _load():
         lib.oracle_compress_bound.argtypes = [_i64, _i64]
         lib.oracle_compress_fp16.restype = _i64
         lib.oracle_compress_fp16.argtypes = [_u16p, _i64, _i64, _u16p, _u8p, _i32p, ctypes.POINTER(_i64)]
+        lib.oracle_compress_16.restype = _i64
+        lib.oracle_compress_16.argtypes = [_u16p, _i64, _i64, _u16p, _u8p, _i32p, ctypes.POINTER(_i64), ctypes.c_uint16]
         lib.oracle_decompress_fp16.restype = None
         lib.oracle_decompress_fp16.argtypes = [_u16p, _u8p, _i32p, _i64, _i64, _u16p]
         lib.oracle_spmv_fp16.restype = None
@@ -118,8 +131,9 @@ def num_threads() -> int:
     return int(_load().oracle_num_threads())
 
 
-def compress(dense):
-    """Oracle compress: (values u16[P], deltas u8[P/2], row_indices i32[R+1], R, C)."""
+def compress(dense, bf16: bool = False):
+    """Oracle compress: (values u16[P], deltas u8[P/2], row_indices i32[R+1], R, C).
+    `bf16`: the 16-bit patterns are bfloat16 (only the NaN test differs)."""
     lib = _load()
     dense = _as_u16(dense)
     assert dense.ndim == 2
@@ -129,10 +143,10 @@ def compress(dense):
     deltas = np.empty(bound // 2, dtype=np.uint8)
     ri = np.empty(rows + 1, dtype=np.int32)
     n = _i64(0)
-    padded = int(lib.oracle_compress_fp16(
+    padded = int(lib.oracle_compress_16(
         dense.ctypes.data_as(_u16p), rows, cols,
         values.ctypes.data_as(_u16p), deltas.ctypes.data_as(_u8p), ri.ctypes.data_as(_i32p),
-        ctypes.byref(n)))
+        ctypes.byref(n), 0x7F80 if bf16 else 0x7C00))
     return values[:padded].copy(), deltas[: padded // 2].copy(), ri, rows, cols
 
 
@@ -190,6 +204,53 @@ def spmv(compressed, x):
                          ri.ctypes.data_as(_i32p), rows, cols, x.ctypes.data_as(_u16p),
                          y64.ctypes.data_as(_f64p), yh.ctypes.data_as(_u16p), l1.ctypes.data_as(_f64p))
     return y64, yh, l1
+
+
+def bf16_bits_to_f64(bits) -> np.ndarray:
+    """float64 values of bfloat16 bit patterns (a bf16 is the upper half of a float32)."""
+    b = np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16
+    return b.view(np.float32).astype(np.float64)
+
+
+def spmv_bf16(compressed, x):
+    """(y float64[R], row L1 mass float64[R]) for bfloat16 values and x: the decode of `decompress`
+    (kernels.cuh:86-108 index rule) followed by a float64 product; pads and dropped zeros add nothing."""
+    dense = bf16_bits_to_f64(decompress(compressed))
+    xv = bf16_bits_to_f64(x)
+    return dense @ xv, np.abs(dense) @ np.abs(xv)
+
+
+def plan_model(deltas, row_indices, seg: int = 1024):
+    """Restatement of the launch plan (macko_spmv_b200/csrc/plan.cuh) for the tests: rows cut into virtual
+    rows of at most `seg` stored elements, each (begin, length, column sum in front, destination), stably
+    sorted by length class, longest first. Returns (desc0 i64[V], desc1 i64[V], out i64[V], seg_first i64[R+1])
+    in sorted order. The reference has no such structure; this checks the GPU builder against its definition."""
+    ri = np.asarray(row_indices, dtype=np.int64)
+    d8 = np.asarray(deltas, dtype=np.uint8)
+    nib = np.empty(d8.size * 2, dtype=np.int64)
+    nib[0::2] = d8 & 15
+    nib[1::2] = d8 >> 4
+    adv = np.concatenate([[0], np.cumsum(nib + 1)])   # adv[k] = sum of (delta + 1) over elements < k
+    begin, length, colsum, out, seg_first = [], [], [], [], [0]
+    for r in range(ri.size - 1):
+        b, e = int(ri[r]), int(ri[r + 1])
+        if e <= b:
+            begin.append(b); length.append(0); colsum.append(0); out.append(r)
+            seg_first.append(seg_first[-1] + 1)
+            continue
+        a0 = b & ~7
+        n = -(-(e - a0) // seg)
+        first = seg_first[-1]
+        for j in range(n):
+            sb, se = max(b, a0 + j * seg), min(e, a0 + (j + 1) * seg)
+            begin.append(sb); length.append(se - sb); colsum.append(int(adv[sb] - adv[b]))
+            out.append(r if n == 1 else (1 << 31) | (first + j))
+        seg_first.append(first + n)
+    begin = np.array(begin, dtype=np.int64); length = np.array(length, dtype=np.int64)
+    colsum = np.array(colsum, dtype=np.int64); out = np.array(out, dtype=np.int64)
+    cls = np.minimum(((begin & 7) + length + 63) >> 6, 63)
+    order = np.argsort(-cls, kind="stable")
+    return begin[order], (length | (colsum << 12))[order], out[order], np.array(seg_first, dtype=np.int64)
 
 
 def dense_matvec(dense, x) -> np.ndarray:

@@ -96,6 +96,11 @@ static inline uint16_t f2h(float f)
 /* Value bits written for a stored element whose source bits are h:
  * identical bits except that NaNs are canonicalised (see f2h). */
 static inline uint16_t stored_bits(uint16_t h) { return h_is_nan(h) ? 0x7fffu : h; }
+/* The same for a value type whose +infinity has the bits `nan_above` (0x7c00 fp16, 0x7f80 bfloat16). */
+static inline uint16_t stored_bits_typed(uint16_t h, uint16_t nan_above)
+{
+    return ((h & 0x7fffu) > nan_above) ? 0x7fffu : h;
+}
 
 /* ---- compress ------------------------------------------------------------ */
 
@@ -127,22 +132,44 @@ int64_t oracle_compress_bound(int64_t rows, int64_t cols)
  * elements / half that many bytes and are fully defined up to the returned
  * padded count P (tail is zero). Returns P; *n_out receives the unpadded count.
  */
+int64_t oracle_compress_16(const uint16_t *dense, int64_t rows, int64_t cols,
+                           uint16_t *values, uint8_t *deltas, int32_t *row_indices,
+                           int64_t *n_out, uint16_t nan_above);
+
 int64_t oracle_compress_fp16(const uint16_t *dense, int64_t rows, int64_t cols,
                              uint16_t *values, uint8_t *deltas, int32_t *row_indices,
                              int64_t *n_out)
 {
-    /* pass 1: per-row counts -> prefix */
+    return oracle_compress_16(dense, rows, cols, values, deltas, row_indices, n_out, 0x7c00u);
+}
+
+/* The same layout for any 16-bit value type that shares fp16's +-0 encoding (bfloat16): the reference
+ * format does not depend on the meaning of the value bits beyond "is it zero" and "is it a NaN"
+ * (cpu_compressor.cuh:26-27,36). The reference has no bf16 encoder: this branch is unpinned against it
+ * except through the fp16 path it shares every line with. */
+int64_t oracle_compress_16(const uint16_t *dense, int64_t rows, int64_t cols,
+                           uint16_t *values, uint8_t *deltas, int32_t *row_indices,
+                           int64_t *n_out, uint16_t nan_above)
+{
+    /* pass 1: per-row counts (rows are independent) -> prefix */
     row_indices[0] = 0;
+    int64_t *counts = (int64_t *)malloc((size_t)(rows > 0 ? rows : 1) * sizeof(int64_t));
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) counts[r] = row_stored_count(dense + r * cols, cols);
     int64_t total = 0;
     for (int64_t r = 0; r < rows; ++r) {
-        total += row_stored_count(dense + r * cols, cols);
+        total += counts[r];
         row_indices[r + 1] = (int32_t)total;
     }
+    free(counts);
     int64_t padded = ((total + 7) / 8) * 8;
     memset(values, 0, (size_t)padded * sizeof(uint16_t));
     memset(deltas, 0, (size_t)(padded / 2));
 
-    /* pass 2: emit */
+    /* pass 2: emit. Rows write disjoint value slots; two rows can share a delta byte, so the 4-bit
+     * deltas go to one byte per element first and are packed afterwards. */
+    uint8_t *nib = (uint8_t *)calloc((size_t)(padded > 0 ? padded : 1), 1);
+#pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < rows; ++r) {
         const uint16_t *row = dense + r * cols;
         int64_t k = row_indices[r];
@@ -155,15 +182,18 @@ int64_t oracle_compress_fp16(const uint16_t *dense, int64_t rows, int64_t cols,
              * the zero found there (cpu_compressor.cuh:36 stores the source value) */
             for (int64_t p = prev + 16; p < c; p += 16) {
                 values[k] = row[p];
-                deltas[k >> 1] |= (uint8_t)(15u << (4 * (k & 1)));
+                nib[k] = 15;
                 ++k;
             }
-            values[k] = stored_bits(h);
-            deltas[k >> 1] |= (uint8_t)((gap & 15) << (4 * (k & 1)));
+            values[k] = stored_bits_typed(h, nan_above);
+            nib[k] = (uint8_t)(gap & 15);
             ++k;
             prev = c;
         }
     }
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < padded / 2; ++b) deltas[b] = (uint8_t)(nib[2 * b] | (nib[2 * b + 1] << 4));
+    free(nib);
     if (n_out) *n_out = total;
     return padded;
 }

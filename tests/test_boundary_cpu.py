@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/macko_b200.h but not exported"
         assert n in cabi.SIGNATURES, f"{n} has no ctypes signature in cabi.py"
-    assert lib.macko_version() == 100
+    assert lib.macko_version() == 200
     assert lib.macko_status_string(0) == b"ok"
 
 
@@ -126,3 +126,46 @@ def test_launch_shape_heuristic_table():
     L, D = ctypes.c_int(0), ctypes.c_int(0)
     assert lib.macko_spmv_shape(-1, 1, 0, 148, ctypes.byref(L), ctypes.byref(D)) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_spmv_shape(1, 1, 0, 0, ctypes.byref(L), ctypes.byref(D)) == cabi.ERR_INVALID_ARGUMENT
+
+
+def test_new_entry_points_validate_before_touching_the_device():
+    import ctypes
+
+    lib = cabi.load()
+    a16 = 0x1000
+    # unknown flag bits
+    assert lib.macko_spmv_fp16_ex(a16, a16, a16, 4, 8, 8, a16, a16, 1.0, 0.0, 4, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_spmv_bf16(a16, a16, a16, 4, 8, 8, a16, a16, 1.0, 0.0, 1 << 7, None) == cabi.ERR_INVALID_ARGUMENT
+    # plan: segment length rules, sizes, null pointers
+    assert lib.macko_spmv_plan_bytes(100, 100, 800, 100) == -1
+    assert lib.macko_spmv_plan_bytes(100, 100, 800, 4096) == -1
+    assert lib.macko_spmv_plan_bytes(100, 1 << 21, 800, 0) == -1
+    nbytes = lib.macko_spmv_plan_bytes(100, 100, 800, 0)
+    assert nbytes > 0 and nbytes % 256 == 0
+    info = cabi.PlanInfo()
+    assert lib.macko_spmv_plan(a16, a16, 100, 100, 800, 0, None, nbytes, ctypes.byref(info), None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_spmv_plan(a16, a16, 100, 100, 800, 0, a16, nbytes - 1, ctypes.byref(info), None) == cabi.ERR_WORKSPACE
+    assert lib.macko_spmv_plan(a16, a16, 100, 100, 800, 0, a16 + 4, nbytes, ctypes.byref(info), None) == cabi.ERR_MISALIGNED
+    # planned product: an info that belongs to another matrix is refused
+    info.rows, info.padded_count, info.virtual_rows, info.segment_elements, info.plan_bytes = 100, 800, 100, 1024, nbytes
+    assert lib.macko_spmv_fp16_planned(a16, a16, a16, 101, 100, 800, a16, ctypes.byref(info), a16, a16, 1.0, 0.0, 0, None) \
+        == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_spmv_fp16_planned(a16, a16, a16, 100, 100, 800, None, ctypes.byref(info), a16, a16, 1.0, 0.0, 0, None) \
+        == cabi.ERR_INVALID_ARGUMENT
+    # scatter: flags and world checked first
+    ptrs = (ctypes.c_void_p * 2)(a16, a16)
+    assert lib.macko_spmv_fp16_scatter_ex(a16, a16, a16, 4, 8, 8, a16, ptrs, 0, ptrs, 0, 2, 8, 0, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_spmv_fp16_scatter_ex(a16, a16, a16, 4, 8, 8, a16, ptrs, 0, ptrs, 2, 2, 0, 0, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_peer_wait_limited(None, 2, 10, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_compress_overflow(None, None) == cabi.ERR_INVALID_ARGUMENT
+
+
+def test_plan_model_of_the_oracle_on_the_reference_vector(reference_vectors):
+    import oracle
+
+    c = reference_vectors[0]     # 5 x 32, row_indices [0, 6, 10, 12, 13, 22]
+    d0, d1, out, seg_first = oracle.plan_model(c["deltas"], c["row_indices"], 256)
+    assert list(seg_first) == [0, 1, 2, 3, 4, 5]
+    # one virtual row per row, all in length class 1 except none: natural order is kept (stable)
+    assert sorted(d0.tolist()) == [0, 6, 10, 12, 13] and sorted((d1 & 4095).tolist()) == [1, 2, 4, 6, 9]
+    assert not (d1 >> 12).any() and sorted(out.tolist()) == [0, 1, 2, 3, 4]
