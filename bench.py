@@ -4,23 +4,28 @@
 Workload (own arm, every N): the Llama-2-7B linear-layer sweep -- 4 shapes x 9 densities =
 36 magnitude-pruned fp16 matrices, seeded synthetic stand-ins for the pruned checkpoints the
 reference measured. One step = one SpMV on each of the 36 compressed matrices (at N > 1 every
-matrix is row-sharded over the ranks and each SpMV is followed by the all-gather of y).
-Metric = device time of one step in microseconds (the sum of the 36 SpMV times), lower is
-better. The step touches ~2.7 GB of distinct compressed data, far more than the 126 MB L2,
-so every SpMV streams its matrix from HBM.
+matrix is row-sharded over the ranks, every product delivers its rows of y to all ranks, and the
+step ends when every rank holds every full y). Metric = device time of one step in microseconds
+(the sum of the 36 SpMV times), lower is better. The step touches ~2.7 GB of distinct compressed
+data, far more than the 126 MB L2, so every SpMV streams its matrix from HBM.
 
-Printed JSON line (rank 0): the contract keys plus
+Printed JSON line (rank 0, the last line of stdout): the contract keys plus
+  y_check       every product of the step (and of the large matrices) compared, outside the timed
+                region, with a dense fp32 product of this rank's rows and, at N > 1, bit for bit with
+                the NCCL all-gather path; the run exits non-zero if it fails
   roofline      algorithmic bytes of a step / device time, against the measured HBM copy peak
-  cpu_baseline  the reference's CPU path (compiled reference compressor + dense torch.mv of
-                the decompressed matrix) on a bounded sample, scaled to one step
+  cpu_baseline  the reference's CPU path (compiled reference compressor + dense torch.mv of the
+                decompressed matrix) on a bounded sample, and the reference's own CUDA kernel
+                (compiled for sm_100a) on the same 36 matrices
   e2e           the same step through the public Python API with x coming from pinned host
-                memory and y copied back to the host, every SpMV
-  per_case      per-matrix microseconds, roofline fraction and speed-up over cuBLAS fp16 GEMV
-`--impl reference` times the reference's CPU path alone (rank 0 only).
+                memory and y copied back to the host inside the timed region
+  per_case / sharded_large / skewed / single_4096 / batched / decode   the other configurations
+`--impl reference` times the reference's CPU path alone on all 36 matrices (rank 0 only).
 """
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
 import os
 import statistics
@@ -37,9 +42,12 @@ import torch  # noqa: E402
 METRIC = "spmv_us_sum_llama7b_sweep"
 UNIT = "us"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum over the 36 spmv launches of one step, from the
-# ncu capture summarised in profiles/spmv_sweep_launches.md (None until captured).
-NCU_STEP_TRAFFIC_BYTES = 2730896128
+# DRAM bytes per algorithmic byte of the SpMV kernel, from the profiler capture of one 32000x4096, 50 %
+# matrix (profiles/spmv_kernel_32000x4096_d50.md: dram read + write over algorithmic bytes). The step's
+# traffic is that ratio times its algorithmic bytes: traffic grows in proportion to the stored elements.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.04
+WORKLOAD = ("llama2-7b linear-layer sweep: shapes 4096x4096, 11008x4096, 4096x11008, 32000x4096 x densities "
+            "0.1..0.9, per-row magnitude pruning; one step = one SpMV per matrix (36)")
 
 
 def measured_hbm_peak():
@@ -49,6 +57,15 @@ def measured_hbm_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def load_workloads():
+    """The workload generators, loaded from their file: importing the package would also load its native
+    libraries, which the reference arm must not have in its process."""
+    spec = importlib.util.spec_from_file_location("_macko_workloads", os.path.join(ROOT, "macko_spmv_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 # --------------------------------------------------------------------------- clocks
@@ -95,16 +112,76 @@ class ClockSampler:
             for name, val in zip(names, parts[4:8]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
+        # the sampler runs over the timed regions and the idle gaps between them: the clock under load is the
+        # upper half of the samples
+        busy = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None,
                 "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- helpers
+
+def event_pair():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def time_rotating(launchers, reps):
+    """Mean device microseconds of one launch, cycling through `launchers` (distinct buffers,
+    together larger than L2) so that every launch streams from HBM."""
+    for f in launchers[: min(8, len(launchers))]:
+        f()
+    torch.cuda.synchronize()
+    e0, e1 = event_pair()
+    n = len(launchers)
+    e0.record()
+    for i in range(reps):
+        launchers[i % n]()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / reps
+
+
+def capture(fn, warm=True):
+    """`fn` captured as a CUDA graph, after one eager run on a side stream unless `warm` is False."""
+    if warm:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+def check_against_dense(y_rows, block, x):
+    """True when y (this rank's rows) is within 1e-3 * L1 per row and 5e-3 relative L2 of the dense fp32 product."""
+    ref = block.float() @ x.float()
+    l1 = block.float().abs() @ x.float().abs()
+    err = (y_rows.float() - ref).abs()
+    ok_abs = bool((err <= 1e-3 * l1 + 1e-6).all())
+    nrm = float(ref.norm())
+    ok_l2 = float((y_rows.float() - ref).norm()) <= 5e-3 * nrm + 1e-12
+    return ok_abs and ok_l2
+
+
+def capture_step_graphs(fn, two_halves: bool):
+    """The step as one CUDA graph, or, when it goes through the exchange buffers, as two graphs that use the
+    two halves of those buffers in turn (every call of `fn` switches to the other half)."""
+    graphs = [capture(fn)]
+    if two_halves:
+        graphs.append(capture(fn, warm=False))
+    return graphs
 
 
 # --------------------------------------------------------------------------- workload
 
 def build_sweep(device, rank: int, world: int):
-    """The 36 compressed matrices of the sweep (this rank's row block of each), their x, and
-    the dense matrices at N == 1 (cuBLAS comparator)."""
+    """The 36 compressed matrices of the sweep (this rank's row block of each), their x, and the dense
+    block (kept for the checks and, at N == 1, for the cuBLAS comparison)."""
     import macko_spmv_b200 as macko_spmv
     from macko_spmv_b200 import sharded, workloads
 
@@ -126,28 +203,12 @@ def build_sweep(device, rank: int, world: int):
             x = workloads.dense_vector(cols, seed + 500, device)
             cases.append({
                 "rows": rows, "cols": cols, "density": d, "comp": comp, "x": x,
-                "lo": lo, "hi": hi, "dense": block if world == 1 else None,
+                "lo": lo, "hi": hi, "dense": block,
                 "bytes": workloads.algorithmic_bytes(comp[0].numel(), hi - lo, cols),
                 "dense_bytes": workloads.dense_bytes(hi - lo, cols),
             })
             del M
     return cases, t_compress, dense_in_bytes
-
-
-def time_rotating(launchers, reps):
-    """Mean device microseconds of one launch, cycling through `launchers` (distinct buffers,
-    together larger than L2) so that every launch streams from HBM."""
-    for f in launchers[: min(8, len(launchers))]:
-        f()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n = len(launchers)
-    e0.record()
-    for i in range(reps):
-        launchers[i % n]()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1000.0 / reps
 
 
 def per_case_numbers(cases, lib, peak_gbs):
@@ -166,8 +227,8 @@ def per_case_numbers(cases, lib, peak_gbs):
 
         def mk(cc, xx, yy):
             args = (cc[0].data_ptr(), cc[1].data_ptr(), cc[2].data_ptr(), rows_l, c["cols"], cc[0].numel(),
-                    xx.data_ptr(), yy.data_ptr(), 1.0, 0.0, stream)
-            return lambda: cabi.check(lib, lib.macko_spmv_fp16(*args))
+                    xx.data_ptr(), yy.data_ptr(), 1.0, 0.0, cabi.SPMV_MATRIX_IMMUTABLE, stream)
+            return lambda: cabi.check(lib, lib.macko_spmv_fp16_ex(*args))
 
         reps = max(30, min(300, int(1.5e9 / c["bytes"])))
         us = time_rotating([mk(a, b, y) for a, b, y in zip(copies, xs, ys)], reps)
@@ -189,11 +250,11 @@ def per_case_numbers(cases, lib, peak_gbs):
 # --------------------------------------------------------------------------- large row-sharded matrices
 
 def sharded_large_leg(device, rank, world, lib, peer, peak_gbs, reps=40):
-    """The two large shapes (12288x49152, 49152x12288; Bernoulli masks at densities 0.1 and 0.5),
-    each rank holding a contiguous row block, the full y delivered to every rank. The four products
-    run back to back (together they stream more than L2 holds on every rank up to 8 GPUs), timed per
-    product with CUDA events, max over ranks. At one GPU the cuBLAS fp16 GEMV on the dense matrix is
-    timed beside each."""
+    """The two large shapes (12288x49152, 49152x12288; Bernoulli masks at densities 0.1 and 0.5), each rank
+    holding a contiguous row block, the full y delivered to every rank. The four products run back to back
+    (together they stream more than L2 holds on every rank up to 8 GPUs) as one CUDA graph, max over ranks;
+    per-product times come from eager launches between events. Every full y is checked first. At one GPU the
+    cuBLAS fp16 GEMV on the dense matrix is timed beside each product, and the planned launch as well."""
     import torch.distributed as dist
 
     import macko_spmv_b200 as macko_spmv
@@ -214,71 +275,92 @@ def sharded_large_leg(device, rank, world, lib, peer, peak_gbs, reps=40):
             if world == 1:
                 for _ in range(3):
                     torch.mv(block, x)
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0, e1 = event_pair()
                 e0.record()
                 for _ in range(10):
                     torch.mv(block, x)
                 e1.record()
                 torch.cuda.synchronize()
                 gemv_us = e0.elapsed_time(e1) * 100.0
-                ref = block.float() @ x.float()
-            cases.append({"rows": rows, "cols": cols, "density": d, "x": x, "gemv_us": gemv_us,
-                          "shard": sharded.RowShard(comp, lo, hi, rows, blocks),
+            cases.append({"rows": rows, "cols": cols, "density": d, "x": x, "gemv_us": gemv_us, "lo": lo, "hi": hi,
+                          "shard": sharded.RowShard(comp, lo, hi, rows, blocks), "block": block,
+                          "frozen": macko_spmv.freeze(comp, plan=True) if world == 1 else None,
                           "y": torch.empty(rows, dtype=torch.float16, device=device) if world == 1 else None,
-                          "ref": ref if world == 1 else None,
                           "bytes": workloads.algorithmic_bytes(comp[0].numel(), hi - lo, cols)})
-            del block
+    torch.cuda.empty_cache()
+    flag = cabi.SPMV_MATRIX_IMMUTABLE
+
+    def step(planned=False):
+        if peer is not None:
+            peer.begin_step()
+            ys = [peer.multiply_deferred(c["shard"], c["x"], immutable=True) for c in cases]
+            peer.wait()
+            return ys
+        stream = torch.cuda.current_stream().cuda_stream   # read at call time: differs under graph capture
+        for c in cases:
+            if planned:
+                macko_spmv.multiply(c["frozen"], c["x"])
+            else:
+                comp = c["shard"].compressed
+                cabi.check(lib, lib.macko_spmv_fp16_ex(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4],
+                                                       comp[0].numel(), c["x"].data_ptr(), c["y"].data_ptr(), 1.0, 0.0, flag, stream))
+        return [c["y"] for c in cases]
+
+    # ---- check every full y (outside any timed region)
+    ys = step()
+    torch.cuda.synchronize()
+    ok = True
+    for c, y in zip(cases, ys):
+        ok = ok and check_against_dense(y[c["lo"]:c["hi"]], c["block"], c["x"])
+        if world > 1:
+            ok = ok and torch.equal(y, sharded.multiply_sharded(c["shard"], c["x"]))
+        if world == 1:
+            ok = ok and check_against_dense(macko_spmv.multiply(c["frozen"], c["x"]), c["block"], c["x"])
+    for c in cases:
+        c["block"] = None
     torch.cuda.empty_cache()
 
-    def product(c):
-        sh = c["shard"]
-        if peer is not None:
-            return peer.multiply(sh, c["x"])
-        comp = sh.compressed
-        stream = torch.cuda.current_stream().cuda_stream   # read at call time: differs under graph capture
-        cabi.check(lib, lib.macko_spmv_fp16(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4],
-                                            comp[0].numel(), c["x"].data_ptr(), c["y"].data_ptr(), 1.0, 0.0, stream))
-        if world > 1:
-            raise RuntimeError("sharded leg needs the peer exchange")
-        return c["y"]
-
-    for _ in range(3):
-        for c in cases:
-            product(c)
-    torch.cuda.synchronize()
-    # the four products as one CUDA graph: device time of a cycle without host launch overhead
-    graph_us = None
-    try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for c in cases:
-                product(c)
-        for _ in range(3):
-            graph.replay()
+    def time_graphs(graphs):
+        for i in range(4):
+            graphs[i % len(graphs)].replay()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0, e1 = event_pair()
         e0.record()
-        for _ in range(reps):
-            graph.replay()
+        for i in range(reps):
+            graphs[i % len(graphs)].replay()
         e1.record()
         torch.cuda.synchronize()
         t = torch.tensor([e0.elapsed_time(e1) * 1000.0 / reps], device=device)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        graph_us = float(t.item())
-    except Exception:   # capture refused: the eager figures below still stand
-        graph_us = None
-    torch.cuda.synchronize()
+        return float(t.item())
+
+    graphs = capture_step_graphs(step, peer is not None)
+    graph_us = time_graphs(graphs)
+    planned_us = None
+    if world == 1:
+        planned_us = time_graphs([capture(lambda: step(planned=True))])
     if world > 1:
         dist.barrier()
+    # per-product times: eager launches between events (they include host launch gaps for short products)
     marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(cases) + 1)] for _ in range(reps)]
     for r in range(reps):
+        if peer is not None:
+            peer.begin_step()
         marks[r][0].record()
         for i, c in enumerate(cases):
-            product(c)
+            if peer is not None:
+                peer.multiply_deferred(c["shard"], c["x"], immutable=True)
+            else:
+                comp = c["shard"].compressed
+                cabi.check(lib, lib.macko_spmv_fp16_ex(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4],
+                                                       comp[0].numel(), c["x"].data_ptr(), c["y"].data_ptr(), 1.0, 0.0, flag,
+                                                       torch.cuda.current_stream().cuda_stream))
             marks[r][i + 1].record()
+        if peer is not None:
+            peer.wait()
     torch.cuda.synchronize()
     us = torch.tensor([[marks[r][i].elapsed_time(marks[r][i + 1]) * 1000.0 for i in range(len(cases))] for r in range(reps)],
                       device=device).mean(dim=0)
@@ -289,15 +371,113 @@ def sharded_large_leg(device, rank, world, lib, peer, peak_gbs, reps=40):
         row = {"shape": [c["rows"], c["cols"]], "density": c["density"], "us": round(t, 2),
                "per_gpu_roofline_frac": round(c["bytes"] / (t * 1e-6) / 1e9 / peak_gbs, 4)}
         if world == 1:
-            err = float((c["y"].float() - c["ref"]).norm() / c["ref"].norm())
-            assert err < 5e-3, f"large-matrix product is wrong (rel L2 {err})"
             row["cublas_gemv_us"] = round(c["gemv_us"], 2)
             row["speedup_vs_cublas"] = round(c["gemv_us"] / t, 3)
+            row["plan_recommended"] = bool(c["frozen"].plan_meta[4])
         out.append(row)
     total_bytes = sum(c["bytes"] for c in cases)
-    return {"cases": out, "us_sum_eager": round(sum(r["us"] for r in out), 2),
-            "us_sum_graph": None if graph_us is None else round(graph_us, 2),
-            "per_gpu_roofline_frac_graph": None if graph_us is None else round(total_bytes / (graph_us * 1e-6) / 1e9 / peak_gbs, 4)}
+    return {"cases": out, "us_sum_eager": round(sum(r["us"] for r in out), 2), "us_sum_graph": round(graph_us, 2),
+            "us_sum_graph_planned_launch": None if planned_us is None else round(planned_us, 2),
+            "per_gpu_roofline_frac_graph": round(total_bytes / (graph_us * 1e-6) / 1e9 / peak_gbs, 4),
+            "y_ok": ok}
+
+
+# --------------------------------------------------------------------------- skewed rows, single product
+
+def time_one_matrix(launch, comp, x, reps=None):
+    """Cold microseconds of `launch(comp_copy, x, y)` over rotating copies of the matrix (together > 2 x L2)."""
+    from macko_spmv_b200 import workloads
+
+    rows, cols = comp[3], comp[4]
+    nbytes = workloads.algorithmic_bytes(comp[0].numel(), rows, cols)
+    n_copy = max(2, min(48, int(300e6 / nbytes) + 1))
+    copies = [comp] + [(comp[0].clone(), comp[1].clone(), comp[2].clone(), rows, cols) for _ in range(n_copy - 1)]
+    ys = [torch.empty(rows, dtype=torch.float16, device=x.device) for _ in range(n_copy)]
+    fns = [launch(c, x, y) for c, y in zip(copies, ys)]
+    return time_rotating(fns, reps or max(30, min(300, int(1.5e9 / nbytes)))), nbytes, ys[0]
+
+
+def skewed_leg(device, lib, peak_gbs):
+    """The two skewed-density shapes: rows from empty to fully dense, clustered non-zeros. Default launch,
+    planned launch (what `freeze` picks for such a matrix) and cuBLAS fp16 GEMV on the dense matrix."""
+    import ctypes
+
+    import macko_spmv_b200 as macko_spmv
+    from macko_spmv_b200 import cabi, workloads
+
+    stream = torch.cuda.current_stream().cuda_stream
+    out = []
+    for si, (rows, cols) in enumerate(workloads.SKEWED_SHAPES):
+        M = workloads.skewed_matrix(rows, cols, seed=5000 + si, device=device)
+        x = workloads.dense_vector(cols, 5500 + si, device)
+        comp = macko_spmv.compress(M)
+
+        def plain(c, xx, y):
+            args = (c[0].data_ptr(), c[1].data_ptr(), c[2].data_ptr(), rows, cols, c[0].numel(), xx.data_ptr(), y.data_ptr(),
+                    1.0, 0.0, cabi.SPMV_MATRIX_IMMUTABLE, stream)
+            return lambda: cabi.check(lib, lib.macko_spmv_fp16_ex(*args))
+
+        keep = []
+
+        def planned(c, xx, y):
+            nb = lib.macko_spmv_plan_bytes(rows, cols, c[0].numel(), 0)
+            plan = torch.empty(nb, dtype=torch.uint8, device=device)
+            info = cabi.PlanInfo()
+            cabi.check(lib, lib.macko_spmv_plan(c[1].data_ptr(), c[2].data_ptr(), rows, cols, c[0].numel(), 0, plan.data_ptr(), nb,
+                                                ctypes.byref(info), stream))
+            keep.append((plan, info))
+            args = (c[0].data_ptr(), c[1].data_ptr(), c[2].data_ptr(), rows, cols, c[0].numel(), plan.data_ptr(),
+                    ctypes.byref(info), xx.data_ptr(), y.data_ptr(), 1.0, 0.0, cabi.SPMV_MATRIX_IMMUTABLE, stream)
+            return lambda: cabi.check(lib, lib.macko_spmv_fp16_planned(*args))
+
+        us_plain, nbytes, y_plain = time_one_matrix(plain, comp, x)
+        ok = check_against_dense(y_plain, M, x)
+        us_planned, _, y_planned = time_one_matrix(planned, comp, x)
+        ok = ok and check_against_dense(y_planned, M, x)
+        info = keep[0][1]
+        dense = [M, M.clone()]
+        us_dense = time_rotating([(lambda m=m: torch.mv(m, x)) for m in dense], 40)
+        out.append({"shape": [rows, cols], "stored_elements": comp[0].numel(), "longest_row": info.longest_row,
+                    "virtual_rows": info.virtual_rows, "plan_recommended": bool(info.recommended),
+                    "default_launch_us": round(us_plain, 2), "planned_launch_us": round(us_planned, 2),
+                    "roofline_frac_default": round(nbytes / (us_plain * 1e-6) / 1e9 / peak_gbs, 4),
+                    "roofline_frac_planned": round(nbytes / (us_planned * 1e-6) / 1e9 / peak_gbs, 4),
+                    "cublas_gemv_us": round(us_dense, 2), "y_ok": ok})
+        del M, dense, keep
+        torch.cuda.empty_cache()
+    return out
+
+
+def single_4096_leg(device, lib, peak_gbs):
+    """One 4096x4096 product: values N(0,1), Bernoulli(0.5) mask, x N(0,1), seed 1001 (CPU generator);
+    compress then multiply, checked against the dense fp32 product computed on the CPU."""
+    import macko_spmv_b200 as macko_spmv
+    from macko_spmv_b200 import cabi
+
+    g = torch.Generator().manual_seed(1001)
+    W = torch.randn(4096, 4096, generator=g).half()
+    mask = torch.rand(4096, 4096, generator=g) < 0.5
+    M_cpu = W * mask
+    x_cpu = torch.randn(4096, generator=g).half()
+    M, x = M_cpu.to(device), x_cpu.to(device)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    comp = macko_spmv.compress(M)
+    torch.cuda.synchronize()
+    t_comp = time.perf_counter() - t0
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def plain(c, xx, y):
+        args = (c[0].data_ptr(), c[1].data_ptr(), c[2].data_ptr(), 4096, 4096, c[0].numel(), xx.data_ptr(), y.data_ptr(),
+                1.0, 0.0, cabi.SPMV_MATRIX_IMMUTABLE, stream)
+        return lambda: cabi.check(lib, lib.macko_spmv_fp16_ex(*args))
+
+    us, nbytes, y = time_one_matrix(plain, comp, x)
+    ref = M_cpu.float() @ x_cpu.float()
+    err = float((y.float().cpu() - ref).norm() / ref.norm())
+    return {"shape": [4096, 4096], "density": 0.5, "mask": "Bernoulli", "us_cold": round(us, 2),
+            "roofline_frac": round(nbytes / (us * 1e-6) / 1e9 / peak_gbs, 4), "compress_ms": round(t_comp * 1e3, 3),
+            "rel_l2_vs_cpu_fp32": err, "y_ok": err <= 5e-3}
 
 
 # --------------------------------------------------------------------------- several right-hand sides
@@ -315,7 +495,7 @@ def batched_leg(device):
     def timed(fn, reps=40):
         for _ in range(3):
             fn()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0, e1 = event_pair()
         e0.record()
         for _ in range(reps):
             fn()
@@ -335,35 +515,77 @@ def batched_leg(device):
     return out
 
 
+# --------------------------------------------------------------------------- decode
+
+def decode_leg(device, world, peer_factory, densities, layers, prompt, new_tokens):
+    """Batch-1 decode of the Llama-2-7B architecture (random weights, every linear layer pruned per row and
+    run through `multiply`): tokens per second for each density; 1.0 = dense nn.Linear (cuBLAS), one GPU only."""
+    import torch.distributed as dist
+
+    from macko_spmv_b200 import llama_decode
+
+    out = {"layers": layers, "prompt_tokens": prompt, "new_tokens": new_tokens, "tensor_parallel": world, "tokens_per_s": {}}
+    for d in densities:
+        if d >= 1.0 and world > 1:
+            continue
+        peer = peer_factory() if world > 1 else None
+        with torch.no_grad():
+            model = llama_decode.LlamaDecoder(d, layers=layers, device=device, max_len=prompt + new_tokens, peer=peer)
+            g = torch.Generator(device=device).manual_seed(4001)
+            tokens = torch.randint(0, model.cfg["vocab"], (prompt,), generator=g, device=device)
+            if world > 1:
+                dist.barrier()
+            _, gen_s, _ = llama_decode.generate(model, tokens, new_tokens)
+        if world > 1:
+            t = torch.tensor([gen_s], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            gen_s = float(t.item())
+        out["tokens_per_s"]["dense" if d >= 1.0 else f"d{d}"] = round(new_tokens / gen_s, 1)
+        del model
+        if peer is not None:
+            peer.close()
+        torch.cuda.empty_cache()
+    return out
+
+
 # --------------------------------------------------------------------------- CPU reference path
 
-def cpu_reference_path(steps: int, warmup: int, gpu_cases=None):
-    """The reference's CPU path on a bounded sample of the sweep: the reference compressor
-    (compiled, unmodified; else the oracle port) followed by a dense fp32 torch.mv of the
-    decompressed matrix, on the 4096x4096 layer at the 9 densities. Returns microseconds
-    scaled to a whole step (the sweep has 14.27x the dense elements of the sample)."""
+def cpu_reference_cases(limit_shapes=None):
+    """The reference's CPU path for the sweep: the matrices of the own arm (same seeds; generated on the GPU
+    when one is visible, like the own arm does, else on the CPU), compressed by the reference's own host
+    compressor (compiled, unmodified; else the oracle port), decompressed, and held as dense fp32 for torch.mv."""
     import numpy as np
-    import oracle
-    from macko_spmv_b200 import workloads
 
+    import oracle
+
+    workloads = load_workloads()
     kind = "reference" if oracle.have_reference() else "port"
     compress = oracle.ref_compress if kind == "reference" else oracle.compress
-    rows, cols = workloads.LLAMA7B_SHAPES[0]
+    gen_device = "cuda" if torch.cuda.is_available() else "cpu"
     sample = []
     t_comp = 0.0
-    for di, d in enumerate(workloads.SWEEP_DENSITIES):
-        M = workloads.magnitude_pruned_matrix(rows, cols, d, workloads.sweep_seed(0, di), device="cpu")
-        dense_bits = M.numpy().view(np.uint16)
-        t0 = time.perf_counter()
-        comp = compress(dense_bits)
-        t_comp += time.perf_counter() - t0
-        dec = torch.from_numpy(oracle.decompress(comp).view(np.float16).copy()).float()
-        x = workloads.dense_vector(cols, 77 + di, "cpu").float()
-        sample.append((dec, x))
-    scale = sum(r * c for r, c in workloads.LLAMA7B_SHAPES) / float(rows * cols)
-    ref_gpu = None
-    if gpu_cases is not None and oracle.have_reference_kernel():
-        ref_gpu = reference_gpu_kernel_times(gpu_cases)
+    shapes = list(enumerate(workloads.LLAMA7B_SHAPES))
+    if limit_shapes is not None:
+        shapes = shapes[:limit_shapes]
+    for si, (rows, cols) in shapes:
+        for di, d in enumerate(workloads.SWEEP_DENSITIES):
+            seed = workloads.sweep_seed(si, di)
+            M = workloads.magnitude_pruned_matrix(rows, cols, d, seed, device=gen_device).cpu()
+            x = workloads.dense_vector(cols, seed + 500, gen_device).cpu().float()
+            dense_bits = M.numpy().view(np.uint16)
+            t0 = time.perf_counter()
+            comp = compress(dense_bits)
+            t_comp += time.perf_counter() - t0
+            dec = torch.from_numpy(oracle.decompress(comp).view(np.float16).copy()).float()
+            sample.append((dec, x))
+            del M, dense_bits, comp
+    return sample, t_comp, kind, gen_device
+
+
+def cpu_reference_path(steps: int, warmup: int, limit_shapes=None):
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)   # a launcher may have set OMP_NUM_THREADS=1 for its ranks; this arm is the only one computing
+    sample, t_comp, kind, gen_device = cpu_reference_cases(limit_shapes)
 
     def one_step():
         for dec, x in sample:
@@ -375,13 +597,15 @@ def cpu_reference_path(steps: int, warmup: int, gpu_cases=None):
     for _ in range(steps):
         one_step()
     t_mv = (time.perf_counter() - t0) / steps
+    full = limit_shapes is None
     return {
-        "value": t_mv * 1e6 * scale, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
-        "sample": f"4096x4096 layer at densities 0.1..0.9 ({len(sample)} of 36 matrices), torch.mv fp32 of the "
-                  f"decompressed matrix, scaled x{scale:.2f} by dense elements to the whole sweep",
-        "compress_us": t_comp * 1e6 * scale, "compress_threads": 1,
-        "spmv_plus_compress_us": (t_mv + t_comp) * 1e6 * scale,
-        "reference_gpu_kernel": ref_gpu,
+        "value": t_mv * 1e6, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+        "sample": (f"all {len(sample)} matrices of the sweep" if full else f"{len(sample)} of the 36 matrices (the first {limit_shapes} shapes)")
+                  + ": torch.mv fp32 of the matrix decompressed from the reference compressor's output, every step; "
+                  f"matrices generated on {gen_device} with the own arm's seeds",
+        "complete_workload": full,
+        "compress_us": t_comp * 1e6, "compress_threads": 1,
+        "spmv_plus_compress_us": (t_mv + t_comp) * 1e6,
     }
 
 
@@ -422,8 +646,7 @@ def run_reference_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["value"] / 1000.0,
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32",
         "data": "synthetic",
-        "config": {"workload": "llama2-7b linear-layer sweep: 4 shapes x 9 densities, per-row magnitude pruning "
-                               "(bounded sample, see cpu_baseline.sample)"},
+        "config": {"workload": WORKLOAD},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -445,61 +668,67 @@ def run_own_arm(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.pop("NCCL_DEBUG", None)  # keep NCCL banners off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
 
     import macko_spmv_b200 as macko_spmv
-    from macko_spmv_b200 import cabi
+    from macko_spmv_b200 import cabi, sharded, workloads
 
     lib = cabi.load()
     peak_gbs, peak_kind = measured_hbm_peak()
     cases, t_compress, dense_in_bytes = build_sweep(device, rank, world)
     n_cases = len(cases)
     step_bytes = sum(c["bytes"] for c in cases)
-
-    # ---- one step, captured as a CUDA graph: 36 x (SpMV [+ all-gather of y]) -----------------
-    ys_local = [torch.empty(c["hi"] - c["lo"], dtype=torch.float16, device=device) for c in cases]
-    ys_full = [torch.empty(c["rows"], dtype=torch.float16, device=device) for c in cases] if world > 1 else ys_local
-    from macko_spmv_b200 import sharded
-
     shards = [sharded.RowShard(c["comp"], c["lo"], c["hi"], c["rows"],
                                [sharded.row_block(c["rows"], r, world) for r in range(world)]) for c in cases]
+    rows8 = lambda r: (r + 7) // 8 * 8
+    step_rows = max(sum(rows8(c["rows"]) for c in cases), sum(rows8(r) for r, _ in workloads.SHARDED_SHAPES) * 2)
     peer = None
     if world > 1 and args.exchange == "peer":
-        from macko_spmv_b200 import workloads
-        peer = sharded.PeerGather(max([c["rows"] for c in cases] + [r for r, _ in workloads.SHARDED_SHAPES]), device)
+        peer = sharded.PeerGather(max(c["rows"] for c in cases), device, step_rows=step_rows)
+    ys_local = [torch.empty(c["hi"] - c["lo"], dtype=torch.float16, device=device) for c in cases]
+    ys_full = [torch.empty(c["rows"], dtype=torch.float16, device=device) for c in cases] if world > 1 else ys_local
+    flag = cabi.SPMV_MATRIX_IMMUTABLE   # the matrices are weights: compressed at set-up, never written again
 
-    def step_eager():
+    def step_device():
+        """One step on the device: N == 1 the C ABI product per matrix; N > 1 the product with the exchange fused
+        into it (every rank's slice stored into all ranks' y, arrival published, no wait) and one bounded wait
+        for all 36 at the end, or (--exchange nccl) product + all-gather per matrix."""
+        if peer is not None:
+            peer.begin_step()
+            out = [peer.multiply_deferred(sh, c["x"], immutable=True) for sh, c in zip(shards, cases)]
+            peer.wait()
+            return out
         stream = torch.cuda.current_stream().cuda_stream
-        if peer is not None:   # SpMV with the exchange fused into its epilogue, then the flag wait
-            for sh, c in zip(shards, cases):
-                peer.multiply(sh, c["x"])
-            return
         for c, yl, yf in zip(cases, ys_local, ys_full):
             comp = c["comp"]
-            cabi.check(lib, lib.macko_spmv_fp16(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(),
-                                                c["hi"] - c["lo"], c["cols"], comp[0].numel(),
-                                                c["x"].data_ptr(), yl.data_ptr(), 1.0, 0.0, stream))
-            if world > 1 and peer is None:
+            cabi.check(lib, lib.macko_spmv_fp16_ex(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(),
+                                                   c["hi"] - c["lo"], c["cols"], comp[0].numel(),
+                                                   c["x"].data_ptr(), yl.data_ptr(), 1.0, 0.0, flag, stream))
+            if world > 1:
                 dist.all_gather_into_tensor(yf, yl)
+        return ys_full
 
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        step_eager()
-    torch.cuda.current_stream().wait_stream(side)
+    # ---- every y of the step checked before anything is timed --------------------------------------
+    ys = step_device()
     torch.cuda.synchronize()
-    graph = None
+    ok = True
+    for c, sh, y in zip(cases, shards, ys):
+        ok = ok and check_against_dense(y[c["lo"]:c["hi"]], c["dense"], c["x"])
+        if world > 1 and peer is not None:
+            ok = ok and torch.equal(y, sharded.multiply_sharded(sh, c["x"]))
+    y_cases = n_cases
+
+    # ---- the step as CUDA graph(s): at N > 1 two graphs, one per half of the exchange buffers ------
+    graphs = None
     try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step_eager()
-        run_step = graph.replay
+        graphs = capture_step_graphs(step_device, peer is not None)
+        run_step = lambda i: graphs[i % len(graphs)].replay()
     except Exception:  # a collective that cannot be captured: time eager launches instead
-        graph = None
-        run_step = step_eager
-    for _ in range(max(args.warmup, 3)):
-        run_step()
+        graphs = None
+        run_step = lambda i: step_device()
+    used_graph = graphs is not None
+    for i in range(max(args.warmup, 3)):
+        run_step(i)
     torch.cuda.synchronize()
 
     sampler = ClockSampler(local_rank)
@@ -508,10 +737,10 @@ def run_own_arm(args):
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = event_pair()
     e0.record()
-    for _ in range(args.steps):
-        run_step()
+    for i in range(args.steps):
+        run_step(i)
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -523,46 +752,77 @@ def run_own_arm(args):
         ms_total = float(t.item())
     ms_per_step = ms_total / args.steps
 
+    # the same step without the immutable-matrix flag (N == 1), for comparison
+    plain_us = None
+    if world == 1:
+        def step_plain():
+            stream = torch.cuda.current_stream().cuda_stream
+            for c, yl in zip(cases, ys_local):
+                comp = c["comp"]
+                cabi.check(lib, lib.macko_spmv_fp16(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), c["rows"], c["cols"],
+                                                    comp[0].numel(), c["x"].data_ptr(), yl.data_ptr(), 1.0, 0.0, stream))
+        gp = capture(step_plain)
+        for _ in range(3):
+            gp.replay()
+        e0.record()
+        for _ in range(args.steps):
+            gp.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        plain_us = e0.elapsed_time(e1) * 1000.0 / args.steps
+        del gp
+
     # ---- end to end through the public API with host buffers ------------------------------------
+    # Every step: x of all 36 products from pinned host memory (one arena, one copy), the products through
+    # macko_spmv_b200.multiply on views of the device arena, every y back to pinned host memory (one copy).
+    x_off, y_off = [0], [0]
+    for c in cases:
+        x_off.append(x_off[-1] + rows8(c["cols"]))
+        y_off.append(y_off[-1] + rows8(c["rows"]))
+    x_host = torch.zeros(x_off[-1], dtype=torch.float16).pin_memory()
+    for c, o in zip(cases, x_off):
+        x_host[o:o + c["cols"]] = c["x"].cpu()
+    x_dev = torch.empty(x_off[-1], dtype=torch.float16, device=device)
+    y_dev = torch.zeros(y_off[-1], dtype=torch.float16, device=device)
+    y_host = torch.zeros(max(y_off[-1], step_rows), dtype=torch.float16).pin_memory()
+    frozen = [macko_spmv.freeze(c["comp"], plan=False) for c in cases]
+
+    def step_e2e():
+        x_dev.copy_(x_host, non_blocking=True)
+        if peer is not None:
+            peer.begin_step()
+            for c, sh, o in zip(cases, shards, x_off):
+                peer.multiply_deferred(sh, x_dev[o:o + c["cols"]], immutable=True)
+            peer.wait()
+            half = peer.buf[peer._half]
+            y_host[: half.numel()].copy_(half, non_blocking=True)
+        elif world > 1:
+            for c, sh, o, yo in zip(cases, shards, x_off, y_off):
+                sharded.multiply_sharded(sh, x_dev[o:o + c["cols"]], out=y_dev[yo:yo + c["rows"]])
+            y_host[: y_dev.numel()].copy_(y_dev, non_blocking=True)
+        else:
+            for c, fz, o, yo in zip(cases, frozen, x_off, y_off):
+                macko_spmv.multiply(fz, x_dev[o:o + c["cols"]], out=y_dev[yo:yo + c["rows"]])
+            y_host[: y_dev.numel()].copy_(y_dev, non_blocking=True)
+
     xs_host = [c["x"].cpu().pin_memory() for c in cases]
     ys_host = [torch.empty(c["rows"], dtype=torch.float16).pin_memory() for c in cases]
-    def step_e2e():
-        for c, sh, xh, yh in zip(cases, shards, xs_host, ys_host):
+
+    def step_e2e_per_product_copies():
+        for c, xh, yh in zip(cases, xs_host, ys_host):
             xd = xh.to(device, non_blocking=True)
-            if world == 1:
-                y = macko_spmv.multiply(c["comp"], xd)
-            elif peer is not None:
-                y = peer.multiply(sh, xd)
-            else:
-                y = sharded.multiply_sharded(sh, xd)
-            yh.copy_(y, non_blocking=True)
-
-    e2e_branches = [torch.cuda.Stream(device=device) for _ in range(4)]
-
-    def step_e2e_branches():
-        """The same calls, the 36 independent chains spread over four streams forked from and joined back
-        into the current one: captured as a graph, copies of one chain run under the kernels of the others."""
-        main = torch.cuda.current_stream()
-        for st in e2e_branches:
-            st.wait_stream(main)
-        for i, (c, xh, yh) in enumerate(zip(cases, xs_host, ys_host)):
-            with torch.cuda.stream(e2e_branches[i % len(e2e_branches)]):
-                xd = xh.to(device, non_blocking=True)
-                y = macko_spmv.multiply(c["comp"], xd)
-                yh.copy_(y, non_blocking=True)
-        for st in e2e_branches:
-            main.wait_stream(st)
+            yh.copy_(macko_spmv.multiply(c["comp"], xd), non_blocking=True)
 
     def time_e2e(run):
-        for _ in range(3):
-            run()
+        for i in range(4):
+            run(i)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        n = max(3, min(args.steps, 20))
+        n = max(4, min(args.steps, 20))
         e0.record()
-        for _ in range(n):
-            run()
+        for i in range(n):
+            run(i)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / n
@@ -572,82 +832,124 @@ def run_own_arm(args):
             ms = float(t.item())
         return ms
 
-    e2e_eager_ms = time_e2e(step_e2e)
-    # The same 36 chains of public-API calls captured once as a CUDA graph (the pinned host buffers are read
-    # and written by every replay), which is how a caller with a fixed set of layers removes the host cost of
-    # 108 asynchronous calls per step.
-    def capture_and_time(step):
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            step()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            step()
-        for yh in ys_host:
-            yh.zero_()
-        ms = time_e2e(g.replay)
-        c = cases[4]   # the replay really delivers y to the host buffers
-        ref = c["dense"].float() @ c["x"].float()
-        err = float((ys_host[4].to(device).float() - ref).norm() / ref.norm())
-        assert err < 5e-3, f"graph replay of the end-to-end step produced a wrong result (rel L2 {err})"
-        return ms, g
-
-    e2e_graph_ms = e2e_forked_ms = None
-    if world == 1:   # ranks must not disagree on whether a capture worked: the row-sharded runs stay eager
-        try:
-            e2e_graph_ms, _g1 = capture_and_time(step_e2e)
-            e2e_forked_ms, _g2 = capture_and_time(step_e2e_branches)
-        except AssertionError:
-            raise
-        except Exception:   # a capture the runtime refuses: the eager figure stands
-            pass
+    e2e_eager_ms = time_e2e(lambda i: step_e2e())
+    e2e_graph_ms = None
+    try:
+        ge = capture_step_graphs(step_e2e, peer is not None)
+        y_host.zero_()
+        e2e_graph_ms = time_e2e(lambda i: ge[i % len(ge)].replay())
+        del ge
+    except Exception:   # a capture the runtime refuses: the eager figure stands
+        e2e_graph_ms = None
+    # what arrived on the host is the step's y (product 4 and the last one, this rank's rows)
+    torch.cuda.synchronize()
+    for k in (4, n_cases - 1):
+        c = cases[k]
+        if peer is not None:
+            o = sum(rows8(cc["rows"]) for cc in cases[:k])
+        else:
+            o = y_off[k]
+        got = y_host[o:o + c["rows"]].to(device)
+        ok = ok and check_against_dense(got[c["lo"]:c["hi"]], c["dense"], c["x"])
     e2e_ms = e2e_eager_ms if e2e_graph_ms is None else min(e2e_eager_ms, e2e_graph_ms)
+    e2e_per_product_ms = time_e2e(lambda i: step_e2e_per_product_copies()) if world == 1 else None
     clocks = sampler.stop() if rank == 0 else None
 
-    # correctness spot check of what was timed (dense fp32 product, N == 1)
-    if world == 1:
-        c = cases[4]
-        ref = c["dense"].float() @ c["x"].float()
-        err = float((ys_local[4].float() - ref).norm() / ref.norm())
-        assert err < 5e-3, f"timed kernel produced a wrong result (rel L2 {err})"
-
     per_case = per_case_numbers(cases, lib, peak_gbs) if (world == 1 and not args.no_per_case) else None
+    ref_gpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        import oracle
+        if oracle.have_reference_kernel():
+            ref_gpu = reference_gpu_kernel_times(cases)
+    for c in cases:
+        c["dense"] = None
+    torch.cuda.empty_cache()
+
     large = None
     if not args.no_sharded_large and (world == 1 or peer is not None):
         large = sharded_large_leg(device, rank, world, lib, peer, peak_gbs)
+        ok = ok and large.pop("y_ok")
+        y_cases += len(large["cases"])
+    skewed = skewed_leg(device, lib, peak_gbs) if (world == 1 and not args.no_skewed) else None
+    single = single_4096_leg(device, lib, peak_gbs) if world == 1 else None
+    if skewed is not None:
+        ok = ok and all(s["y_ok"] for s in skewed)
+    if single is not None:
+        ok = ok and single["y_ok"]
     batched = batched_leg(device) if (world == 1 and not args.no_batched) else None
-    cpu_base = cpu_reference_path(3, 1, gpu_cases=cases) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
 
+    # ---- peer error flag and verdict of the checks, over all ranks ------------------------------
+    peer_flag = peer.error_flag() if peer is not None else 0
+    verdict = torch.tensor([1 if ok else 0, -peer_flag], device=device, dtype=torch.int64)
+    if world > 1:
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    ok_all, peer_flag_all = bool(verdict[0].item()), int(-verdict[1].item())
+
+    decode = None
+    if not args.no_decode:
+        del graphs
+        graphs = None
+        dens = (0.5, 0.1, 1.0) if world == 1 else (0.5, 0.1)
+        cfg_rows = max(3 * 4096, 2 * 11008, 32000)
+        decode = decode_leg(device, world, lambda: sharded.PeerGather(cfg_rows, device), dens, args.decode_layers,
+                            args.decode_prompt, args.decode_tokens)
+
+    cpu_base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_base = cpu_reference_path(3, 1, limit_shapes=1)   # bounded: the 4096x4096 layer at the 9 densities
+        scale = sum(r * c for r, c in workloads.LLAMA7B_SHAPES) / float(4096 * 4096)
+        cpu_base["value_sample_us"] = cpu_base["value"]
+        cpu_base["value"] = cpu_base["value"] * scale
+        cpu_base["sample"] += f"; value = the sample's time x {scale:.2f} (dense elements of the whole sweep over the sample's)"
+        if ref_gpu is not None:
+            cpu_base["reference_gpu_kernel_sum_us"] = ref_gpu["sum_us"]
+            cpu_base["reference_gpu_kernel"] = ref_gpu
+
+    line = None
     if rank == 0:
-        achieved = step_bytes * world / (ms_per_step * 1e-3) / 1e9 if world == 1 else step_bytes / (ms_per_step * 1e-3) / 1e9
+        achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+        launches_per_step = n_cases + (1 if peer is not None else 0)
+        large_fracs = [c["per_gpu_roofline_frac"] for c in large["cases"]] if large else []
+        if per_case:
+            large_fracs += [p["roofline_frac"] for p in per_case if p["shape"][0] * p["shape"][1] >= 8192 * 8192]
         line = {
             "metric": METRIC, "value": ms_per_step * 1000.0, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
             "config": {
-                "workload": "llama2-7b linear-layer sweep: shapes 4096x4096, 11008x4096, 4096x11008, 32000x4096 x "
-                            "densities 0.1..0.9, per-row magnitude pruning; one step = one SpMV per matrix (36)",
-                "parallelism": "single GPU" if world == 1 else (f"rows of every matrix split over {world} GPUs; " + ("every SpMV kernel stores its y slice into all ranks' y over NVLink and ends when all slices have arrived (no collective)" if peer is not None else "NCCL all-gather of y after each SpMV")),
+                "workload": WORKLOAD,
+                "parallelism": "single GPU" if world == 1 else (f"rows of every matrix split over {world} GPUs; " + ("every SpMV kernel stores its y slice into all ranks' y over NVLink and publishes its arrival; one bounded wait per step for all 36 (no collective)" if peer is not None else "NCCL all-gather of y after each SpMV")),
                 "l2": "inputs larger than L2: a step streams %.2f GB of distinct compressed data per GPU, each matrix once" % (step_bytes / 1e9),
-                "launch": "one CUDA graph per step" if graph is not None else "eager launches",
+                "launch": ("one CUDA graph per step" if used_graph else "eager launches")
+                          + "; matrices declared immutable (weights compressed at set-up): first matrix loads may precede the end of the previous kernel",
             },
+            "y_check": {"cases": y_cases, "ok": ok_all, "peer_error_flag": peer_flag_all,
+                        "what": "every product of the step and of the large matrices: this rank's rows against a dense fp32 product "
+                                "(1e-3*L1 per row, 5e-3 relative L2)" + ("; full y bit-equal to the NCCL all-gather path" if peer is not None else "")},
             "roofline": {
                 "bound": "hbm", "achieved": round(achieved, 1), "peak": peak_gbs, "unit": "GB/s",
-                "frac": round(achieved / peak_gbs, 4), "traffic": NCU_STEP_TRAFFIC_BYTES if world == 1 else None,
+                "frac": round(achieved / peak_gbs, 4),
+                "traffic": int(step_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE) if world == 1 else None,
+                "traffic_source": "dram bytes per algorithmic byte (1.04) from the profiler capture of one 32000x4096 50 % product "
+                                  "(profiles/spmv_kernel_32000x4096_d50.md), scaled by the step's algorithmic bytes; not measured in this run",
                 "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_step_per_gpu": step_bytes,
+                "large_matrix_frac_min": round(min(large_fracs), 4) if large_fracs else None,
+                "large_matrix_frac_max": round(max(large_fracs), 4) if large_fracs else None,
+                "step_us_without_immutable_flag": None if plain_us is None else round(plain_us, 2),
                 "note": "bytes = 2.5*P + 4*(rows+1) + 2*cols + 2*rows per SpMV, summed over the step, over the step's device time",
             },
             "e2e": {
                 "value": e2e_ms * 1000.0, "unit": UNIT,
                 "eager_us": e2e_eager_ms * 1000.0, "graph_replay_us": None if e2e_graph_ms is None else e2e_graph_ms * 1000.0,
-                "graph_replay_four_streams_us": None if e2e_forked_ms is None else e2e_forked_ms * 1000.0,
-                "h2d_bytes_per_step": sum(2 * c["cols"] for c in cases),
-                "d2h_bytes_per_step": sum(2 * c["rows"] for c in cases),
-                "api": "macko_spmv_b200.multiply(compressed, x) per matrix; x from pinned host memory, y copied to pinned host memory; compressed matrix resident on the device as the API requires; value = the faster of eager calls and a CUDA-graph replay of the same calls, both on one stream like the device-only figure; graph_replay_four_streams_us spreads the 36 independent chains over four forked streams, where copies and kernels of different chains overlap",
+                "per_product_copies_us": None if e2e_per_product_ms is None else e2e_per_product_ms * 1000.0,
+                "h2d_bytes_per_step": int(x_host.numel() * 2),
+                "d2h_bytes_per_step": int((peer.buf[0].numel() if peer is not None else y_dev.numel()) * 2),
+                "api": "every step: one copy of the step's 36 x vectors from a pinned host arena, macko_spmv_b200.multiply(frozen, x_view, out=y_view) "
+                       "per matrix (N > 1: PeerGather.multiply_deferred + wait), one copy of all y to a pinned host arena; compressed matrices resident "
+                       "on the device as the API requires; value = the faster of eager calls and a CUDA-graph replay of the same calls; "
+                       "per_product_copies_us = the same step with one H2D and one D2H copy per product",
             },
-            "gpu_launches": args.steps * n_cases,
+            "gpu_launches": args.steps * launches_per_step,
             "clocks": clocks,
             "compress": {
                 "seconds_for_sweep": round(t_compress, 4),
@@ -655,6 +957,10 @@ def run_own_arm(args):
                 "note": "GPU compressor, wall clock including the 4-byte size read-back, per-rank blocks",
             },
         }
+        if decode is not None:
+            line["decode"] = decode
+            for k, v in decode["tokens_per_s"].items():
+                line["e2e"][f"decode_tokens_per_s_{k}"] = v
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
         if large is not None:
@@ -664,48 +970,92 @@ def run_own_arm(args):
                 "note": "per-case figures are eager launches between CUDA events (they include host launch gaps when a product is "
                         "shorter than the host's launch path); us_sum_graph replays the four products as one CUDA graph",
                 **large}
+        if skewed is not None:
+            line["skewed"] = skewed
+            line["roofline"]["skewed_frac_planned_min"] = min(s["roofline_frac_planned"] for s in skewed)
+        if single is not None:
+            line["single_4096"] = single
         if batched is not None:
             line["batched"] = batched
         if per_case is not None:
             line["per_case"] = per_case
             sp = [p["speedup_vs_cublas"] for p in per_case]
             line["geomean_speedup_vs_cublas"] = round(float(torch.tensor(sp).log().mean().exp()), 3)
-        print(json.dumps(line), flush=True)
+
+    # ---- tear down in order: graphs, exchange buffers, process group; the result line comes last ----
+    graphs = None
+    torch.cuda.synchronize()
     if world > 1:
-        # Leave without tearing NCCL down: destroying a communicator that a live CUDA graph still
-        # references can block forever, and every result has been printed by now.
-        torch.cuda.synchronize()
         dist.barrier()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
+        if peer is not None:
+            peer.close()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if not ok_all or peer_flag_all != 0:
+        raise SystemExit(f"y_check failed (ok={ok_all}, peer_error_flag={peer_flag_all})")
 
 
 def run_single_case(args):
-    """A few SpMVs on one synthetic matrix: the small workload profiler captures are taken on."""
+    """A few SpMVs on one synthetic matrix: the small workload profiler captures are taken on.
+    `--single-kind`: plain (default launch), planned, batched8, scatter (world of one), decompress, compress."""
+    import ctypes
+
     import macko_spmv_b200 as macko_spmv
-    from macko_spmv_b200 import workloads
+    from macko_spmv_b200 import cabi, workloads
 
     rows, cols, density = args.single.split(",")
     rows, cols, density = int(rows), int(cols), float(density)
     torch.cuda.set_device(0)
-    M = workloads.magnitude_pruned_matrix(rows, cols, density, seed=2999, device="cuda")
+    if args.single_kind == "planned":
+        M = workloads.skewed_matrix(rows, cols, seed=2999, device="cuda", mean_density=density)
+    else:
+        M = workloads.magnitude_pruned_matrix(rows, cols, density, seed=2999, device="cuda")
     x = workloads.dense_vector(cols, 3001, "cuda")
     comp = macko_spmv.compress(M)
+    lib = cabi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    kind = args.single_kind
+    if kind == "plain":
+        run = lambda: macko_spmv.multiply(comp, x)
+    elif kind == "planned":
+        fz = macko_spmv.freeze(comp, plan=True)
+        run = lambda: macko_spmv.multiply(fz, x)
+    elif kind == "batched8":
+        V = torch.stack([x] * 8).contiguous()
+        run = lambda: macko_spmv.multiply_batched(comp, V)[0]
+    elif kind == "scatter":
+        ybuf = torch.zeros(rows, dtype=torch.float16, device="cuda")
+        flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+        ptrs = ctypes.c_void_p * 1
+        yt, ft = ptrs(ybuf.data_ptr()), ptrs(flags.data_ptr())
+
+        def run():
+            cabi.check(lib, lib.macko_spmv_fp16_scatter_ex(comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), rows, cols,
+                                                           comp[0].numel(), x.data_ptr(), yt, 0, ft, 0, 1, 0, 0, stream))
+            return ybuf
+    elif kind == "decompress":
+        run = lambda: macko_spmv.decompress(comp)[:, 0].contiguous()
+    elif kind == "compress":
+        run = lambda: macko_spmv.compress(M)[0][:rows]
+    else:
+        raise SystemExit(f"unknown --single-kind {kind}")
     for _ in range(max(args.warmup, 1)):
-        macko_spmv.multiply(comp, x)
+        run()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = event_pair()
     e0.record()
     for _ in range(args.steps):
-        y = macko_spmv.multiply(comp, x)
+        y = run()
     e1.record()
     torch.cuda.synchronize()
-    ref = M.float() @ x.float()
-    err = float((y.float() - ref).norm() / ref.norm())
     nbytes = workloads.algorithmic_bytes(comp[0].numel(), rows, cols)
-    print(json.dumps({"single": [rows, cols, density], "us_warm_l2": e0.elapsed_time(e1) * 1000 / args.steps,
-                      "algorithmic_bytes": nbytes, "rel_l2_vs_dense_fp32": err}), flush=True)
+    res = {"single": [rows, cols, density], "kind": kind, "us_warm_l2": e0.elapsed_time(e1) * 1000 / args.steps,
+           "algorithmic_bytes": nbytes}
+    if kind in ("plain", "planned", "batched8", "scatter"):
+        ref = M.float() @ x.float()
+        res["rel_l2_vs_dense_fp32"] = float((y.float() - ref).norm() / ref.norm())
+    print(json.dumps(res), flush=True)
 
 
 def main():
@@ -718,10 +1068,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-batched", action="store_true", help="skip the multi-vector product figures")
     ap.add_argument("--no-sharded-large", action="store_true", help="skip the large row-sharded matrices")
+    ap.add_argument("--no-skewed", action="store_true", help="skip the skewed-density matrices")
+    ap.add_argument("--no-decode", action="store_true", help="skip the Llama-architecture decode figures")
+    ap.add_argument("--decode-layers", type=int, default=32)
+    ap.add_argument("--decode-prompt", type=int, default=16)
+    ap.add_argument("--decode-tokens", type=int, default=48)
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how the y slices are exchanged (fused peer stores, or NCCL all-gather)")
     ap.add_argument("--single", default=None, metavar="ROWS,COLS,DENSITY",
-                    help="run only a few SpMVs on one matrix (small case for profiler captures)")
+                    help="run only a few products on one matrix (small case for profiler captures)")
+    ap.add_argument("--single-kind", default="plain",
+                    choices=["plain", "planned", "batched8", "scatter", "decompress", "compress"])
     args = ap.parse_args()
     if args.single:
         run_single_case(args)

@@ -164,13 +164,22 @@ def freeze(compressed_M, plan="auto", segment_elements=0):
     return FrozenMatrix(compressed_M, None, info)
 
 
-def multiply(compressed_M, V):
-    """y = M @ V for a compressed matrix and an fp16 CUDA vector (src/macko_spmv/__init__.py:134-149)."""
+def multiply(compressed_M, V, out=None):
+    """y = M @ V for a compressed matrix and an fp16 CUDA vector (src/macko_spmv/__init__.py:134-149).
+
+    `out` (not in the reference): a contiguous CUDA vector of M_rows elements that receives y, for callers
+    that keep their results in one buffer; without it a new tensor is returned, as in the reference."""
     assert compressed_M[0].is_cuda
     assert compressed_M[1].is_cuda
     assert compressed_M[2].is_cuda
     assert V.is_cuda
     assert V.is_contiguous()
+    if out is not None:
+        frozen = isinstance(compressed_M, FrozenMatrix)
+        torch.ops.macko_spmv.multiply_ex.default(
+            compressed_M[0], compressed_M[1], compressed_M[2], compressed_M[3], compressed_M[4], V, out, 1.0, 0.0,
+            1 if frozen else 0)
+        return out
     if isinstance(compressed_M, FrozenMatrix):
         if compressed_M.plan is not None:
             return torch.ops.macko_spmv.multiply_planned.default(

@@ -29,6 +29,7 @@ struct PlanView {
     float *partial;         // natural order: fp32 sums of the segments of rows cut into several
     const int *seg_first;   // [rows + 1] natural index of the first virtual row of each row
     unsigned *arrived;      // [rows] segments of the row whose partial sum is in; back to 0 when the row is written
+    unsigned *sched;        // [0] blocks handed out beyond every warp's first, [1] warps that have left; both 0 between launches
     int n_virtual;
 };
 

@@ -258,33 +258,33 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     //      list, the direction alternating from round to round (longest first: the ends even out) ------------
     const long long n_warps = (long long)gridDim.x * kWarpsPerCta;
     const long long warp_id = (long long)blockIdx.x * kWarpsPerCta + (tid >> 5);
-    int row_next, row_hi;   // plain: rows [row_next, row_hi); planned: positions in the warp's sequence
-    if constexpr (PLAN) {
-        const int V = extra.plan.n_virtual;
-        const int W = (int)n_warps, w = (int)warp_id;
-        const int nb = (V + K - 1) / K;                 // blocks of K virtual rows
-        const int full_rounds = nb / W;
-        const int rest = nb - full_rounds * W;           // blocks of the last, partly filled round
-        const int slot = (full_rounds & 1) ? W - 1 - w : w;
-        const int count = full_rounds + (slot < rest ? 1 : 0);
-        row_next = 0;
-        row_hi = count * K;
-        if (count > 0) {
-            const int last_round = count - 1;
-            const int last_blk = last_round * W + ((last_round & 1) ? W - 1 - w : w);
-            if (last_blk == nb - 1) row_hi -= nb * K - V;   // the very last block may hold fewer than K
-        }
-    } else {
+    int row_next = 0, row_hi = 0;   // plain: rows [row_next, row_hi) of this warp
+    if constexpr (!PLAN) {
         const long long n_blocks = ((long long)rows + K - 1) / K;
         row_next = (int)min((long long)rows, (n_blocks * warp_id / n_warps) * K);
         row_hi = (int)min((long long)rows, (n_blocks * (warp_id + 1) / n_warps) * K);
     }
-    // sorted index of position p of this warp's sequence (planned)
-    auto sorted_index = [&](int p) -> int {
-        const int W = (int)n_warps, w = (int)warp_id;
-        const int round = p / K;
-        return (round * W + ((round & 1) ? W - 1 - w : w)) * K + (p - round * K);
+    // Planned: the sorted virtual rows are handed out in blocks of K (one per group, similar lengths), longest
+    // first. Block `warp_id` is this warp's first; every further block comes from a counter in the plan
+    // (atomicAdd), fetched one block ahead together with the block's descriptors, so that a warp never waits
+    // for either: longest-first with a shared counter keeps all warps busy until the short rows run out.
+    const int plan_blocks = PLAN ? (extra.plan.n_virtual + K - 1) / K : 0;
+    int nxt_blk = PLAN ? (int)min(warp_id, (long long)plan_blocks) : 0;   // block whose descriptors are in n_*
+    int nn_blk = plan_blocks;                                            // lane 0: the block after that (counter value)
+    int n_b = 0;            // descriptors of block nxt_blk for my group
+    unsigned n_pk = 0u, n_out = 0xffffffffu;
+    auto load_block = [&](int blk) {
+        const int v = blk * K + (lane / L);
+        n_b = 0; n_pk = 0u;
+        n_out = 0xffffffffu;   // no virtual row
+        if (blk < plan_blocks && v < extra.plan.n_virtual) {
+            const uint2 d = __ldg(extra.plan.desc + v);
+            n_b = (int)d.x;
+            n_pk = d.y;
+            n_out = __ldg(extra.plan.out + v);
+        }
     };
+    if constexpr (PLAN) load_block(nxt_blk);
 
     // PEER: rows of the whole CTA (its warps own consecutive ranges) and the staging area for their y
     int cta_row_lo = 0, cta_row_hi = 0;
@@ -296,22 +296,10 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     }
     __half *ystage = reinterpret_cast<__half *>(smem + (((size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) + 15) & ~(size_t)15));
 
-    // Window of 32 row offsets (planned: 32 virtual-row descriptors) held one per lane and read by shuffle.
+    // Window of 32 row offsets held one per lane; entry r of the window is read by shuffle (plain launch).
     int win_base = row_next;
-    int ri_reg = 0;      // plain: ri[win_base + lane]; planned: first stored element of the virtual row
-    unsigned pk_reg = 0; // planned: length | starting column << kPlanLenBits
-    auto load_window = [&]() {
-        if constexpr (PLAN) {
-            const int p = win_base + lane;
-            uint2 d = make_uint2(0u, 0u);
-            if (p < row_hi) d = __ldg(extra.plan.desc + sorted_index(p));
-            ri_reg = (int)d.x;
-            pk_reg = d.y;
-        } else {
-            ri_reg = __ldg(ri + min(win_base + lane, rows));
-        }
-    };
-    if (row_next < row_hi) load_window();
+    int ri_reg = 0;
+    if (!PLAN && row_next < row_hi) ri_reg = __ldg(ri + min(win_base + lane, rows));
 
     // ---- per-group state ------------------------------------------------------------------------------
     constexpr int LOG_STEP = (L == 32) ? 8 : (L == 16) ? 7 : (L == 8) ? 6 : 5;
@@ -335,6 +323,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     for (int b = 0; b < BV; ++b) accb[b][0] = accb[b][1] = 0.f;
 
     bool first_pass = true;
+    bool plan_first = PLAN;
     for (;;) {
         bool done = false;
         // ---- groups that ran out of work finish their row and take the next one ---------------------
@@ -376,48 +365,61 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                     }
                 }
             }
-            const int avail = row_hi - row_next;
-            if (avail <= 0) {
-                if (needmask == 0xffffffffu) done = true;
-                if (need) { my_row = -1; pos = 0; end = 0; begin = 0; }
-            } else {
-                const unsigned leaders = needmask & kLeaders;
-                const int want = __popc(leaders);
-                const int take = min(want, avail);
-                if (row_next + take > win_base + (PLAN ? 32 : 31)) {  // warp-uniform
-                    win_base = row_next;
-                    load_window();
-                }
-                const int rank = __popc(leaders & ((1u << group_lane0) - 1u));
-                const int nr = row_next + rank;
-                // offsets are clamped into [0, stored] so that corrupt row_indices (or a corrupt plan) cannot send
-                // loads outside values/deltas
-                int b, e;
-                unsigned colbase2 = 0u;   // planned: twice the column sum in front of the segment (a byte offset into x)
-                if constexpr (PLAN) {
-                    b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
-                    const unsigned pk = __shfl_sync(0xffffffffu, pk_reg, (nr - win_base) & 31);
-                    e = min(b + (int)(pk & ((1u << kPlanLenBits) - 1u)), stored);
-                    colbase2 = (pk >> kPlanLenBits) << 1;
+            if constexpr (PLAN) {
+                if (needmask != 0xffffffffu) {
+                    // some group of the block is still at work: the others idle until the whole block is done
+                    if (need) { my_row = -1; pos = 0; end = 0; begin = 0; }
+                } else if (nxt_blk >= plan_blocks) {
+                    done = true;
+                    my_row = -1; pos = 0; end = 0; begin = 0;
                 } else {
-                    b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
-                    e = min(__shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31), stored);
-                }
-                if (need) {
-                    if (rank < take) {
-                        if constexpr (PLAN) {
-                            my_row = 0;
-                            out_word = __ldg(extra.plan.out + sorted_index(nr));   // needed only when the virtual row ends
-                        } else {
-                            my_row = nr;
-                        }
-                        begin = b; end = e; pos = b & ~(kGroup - 1);
-                        run = lane_const + colbase2 - 2u * (unsigned)(b & (kGroup - 1));   // the unit that holds `begin` starts before the row
-                    } else {
+                    // adopt the block fetched ahead; offsets are clamped into [0, stored] so that a corrupt plan
+                    // cannot send loads outside values/deltas
+                    const int b = min(max(n_b, 0), stored);
+                    const int e = min(b + (int)(n_pk & ((1u << kPlanLenBits) - 1u)), stored);
+                    out_word = n_out;
+                    if (n_out == 0xffffffffu) {
                         my_row = -1; pos = 0; end = 0; begin = 0;
+                    } else {
+                        my_row = 0;
+                        begin = b; end = e; pos = b & ~(kGroup - 1);
+                        run = lane_const + ((n_pk >> kPlanLenBits) << 1) - 2u * (unsigned)(b & (kGroup - 1));
+                    }
+                    // and fetch ahead again: the next block's descriptors, and the counter for the one after it
+                    if (!first_pass) {
+                        nxt_blk = __shfl_sync(0xffffffffu, nn_blk, 0);
+                        load_block(nxt_blk);
+                        if (lane == 0) nn_blk = (int)atomicAdd(extra.plan.sched, 1u) + (int)n_warps;
                     }
                 }
-                row_next += take;
+            } else {
+                const int avail = row_hi - row_next;
+                if (avail <= 0) {
+                    if (needmask == 0xffffffffu) done = true;
+                    if (need) { my_row = -1; pos = 0; end = 0; begin = 0; }
+                } else {
+                    const unsigned leaders = needmask & kLeaders;
+                    const int want = __popc(leaders);
+                    const int take = min(want, avail);
+                    if (row_next + take > win_base + 31) {  // warp-uniform
+                        win_base = row_next;
+                        ri_reg = __ldg(ri + min(win_base + lane, rows));
+                    }
+                    const int rank = __popc(leaders & ((1u << group_lane0) - 1u));
+                    const int nr = row_next + rank;
+                    // offsets are clamped into [0, stored] so that a corrupt row_indices cannot send loads outside values/deltas
+                    const int b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
+                    const int e = min(__shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31), stored);
+                    if (need) {
+                        if (rank < take) {
+                            my_row = nr; begin = b; end = e; pos = b & ~(kGroup - 1);
+                            run = lane_const - 2u * (unsigned)(b & (kGroup - 1));   // the unit that holds `begin` starts before the row
+                        } else {
+                            my_row = -1; pos = 0; end = 0; begin = 0;
+                        }
+                    }
+                    row_next += take;
+                }
             }
         }
 
@@ -470,18 +472,36 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
 #pragma unroll 1
                 for (int i = kXPadFront + cols + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
                 if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(x);
-                    uint4 *dst = reinterpret_cast<uint4 *>(xs + kXPadFront);
+                    // 16-byte asynchronous copies global -> shared: no registers, all of a thread's copies in flight
+                    // together, and the matrix loads issued above stay in flight beside them
                     const int n_vec = cols >> 3;
-    #pragma unroll 1
-                for (int i = tid; i < n_vec; i += kThreads) dst[i] = __ldg(src + i);
+                    const unsigned dst0 = (unsigned)x_base + 2u * kXPadFront;
+                    const char *src0 = reinterpret_cast<const char *>(x);
+#pragma unroll 1
+                    for (int i = tid; i < n_vec; i += kThreads)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + 16u * (unsigned)i), "l"(src0 + 16 * (size_t)i) : "memory");
 #pragma unroll 1
                     for (int i = (n_vec << 3) + tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
                 } else {
-    #pragma unroll 1
-                for (int i = tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
+#pragma unroll 1
+                    for (int i = tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
                 }
                 __syncthreads();
+            }
+        }
+        if constexpr (PLAN) {
+            if (plan_first) {
+                // The counter belongs to the plan, which the previous kernel of the stream may have been using: it
+                // is first touched here, behind the wait. Two values: the block after this warp's first one (its
+                // descriptors are loaded now, consumed at the next hand-over) and the one after that.
+                plan_first = false;
+                unsigned a0 = 0u;
+                if (lane == 0) a0 = atomicAdd(extra.plan.sched, 1u);
+                nxt_blk = (int)__shfl_sync(0xffffffffu, a0, 0) + (int)n_warps;
+                load_block(nxt_blk);
+                if (lane == 0) nn_blk = (int)atomicAdd(extra.plan.sched, 1u) + (int)n_warps;
             }
         }
         if (done) break;
@@ -596,6 +616,19 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         // every sub-step that was skipped lies behind the end of all rows of the warp: `run` is not used again before the next row resets it
         run += (unsigned)(2 * L * D);
         pos += D * STEP;
+    }
+
+    if constexpr (PLAN) {
+        // The warp that leaves last puts the plan's counters back to zero for the next launch. The fence orders
+        // this warp's last counter update (a value it never used may still be on its way) before its sign-off.
+        if (lane == 0) {
+            __threadfence();
+            const unsigned left = atomicAdd(extra.plan.sched + 1, 1u);
+            if (left == (unsigned)n_warps - 1u) {
+                extra.plan.sched[0] = 0u;
+                extra.plan.sched[1] = 0u;
+            }
+        }
     }
 
     if (PEER) {
@@ -974,6 +1007,7 @@ int macko_spmv_fp16_planned(const void *values, const void *deltas, const int32_
     extra.plan.partial = reinterpret_cast<float *>(base + lay.partial);
     extra.plan.seg_first = reinterpret_cast<const int *>(base + lay.seg_first);
     extra.plan.arrived = reinterpret_cast<unsigned *>(base + lay.arrived);
+    extra.plan.sched = reinterpret_cast<unsigned *>(base + lay.header) + 8;
     extra.plan.n_virtual = info->virtual_rows;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return launch<8, 3, true, false, 1, true>(values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y,

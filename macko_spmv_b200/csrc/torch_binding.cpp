@@ -153,6 +153,28 @@ void multiply_out_cuda(const at::Tensor &values, const at::Tensor &deltas, const
                      "macko_spmv_fp16");
 }
 
+// multiply_out with flag bits (MACKO_SPMV_MATRIX_IMMUTABLE): the product into a caller-owned y.
+void multiply_ex_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
+                      int64_t rows, int64_t cols, const at::Tensor &V, at::Tensor y, double alpha, double beta, int64_t flags)
+{
+    check_compressed(values, deltas, ri, rows, cols);
+    TORCH_CHECK(V.dtype() == values.dtype() && y.dtype() == values.dtype(), "V and y must be torch.half");
+    TORCH_CHECK(V.is_cuda() && V.device() == values.device() && y.device() == values.device(),
+                "V and y must be on the device of M");
+    TORCH_CHECK(V.is_contiguous() && y.is_contiguous(), "V and y must be contiguous");
+    TORCH_CHECK(V.dim() == 1 && V.size(0) == cols && y.dim() == 1 && y.size(0) == rows, "bad vector shapes");
+    const c10::cuda::CUDAGuard guard(values.device());
+    cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
+    if (values.dtype() == at::kBFloat16)
+        check_status(macko_spmv_bf16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                     values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, (uint32_t)flags, stream),
+                     "macko_spmv_bf16");
+    else
+        check_status(macko_spmv_fp16_ex(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                        values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, (uint32_t)flags, stream),
+                     "macko_spmv_fp16_ex");
+}
+
 // Y[batch, rows] for V[batch, cols]: up to 8 vectors per pass over the compressed matrix.
 at::Tensor multiply_batched_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
                                  int64_t rows, int64_t cols, const at::Tensor &V)
@@ -224,6 +246,8 @@ TORCH_LIBRARY(macko_spmv, m)
     m.def("compress_dense(Tensor M) -> (Tensor, Tensor, Tensor)");
     m.def("multiply_batched(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor V) -> Tensor");
     m.def("decompress(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols) -> Tensor");
+    m.def("multiply_ex(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor V, "
+          "Tensor(a!) y, float alpha, float beta, int flags) -> ()");
     m.def("multiply_frozen(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor V) -> Tensor");
     m.def("plan_build(Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, int padded_count, int segment_elements) -> (Tensor, Tensor)");
     m.def("multiply_planned(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor plan, "
@@ -237,6 +261,7 @@ TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
     m.impl("compress_dense", &compress_cuda);
     m.impl("multiply_batched", &multiply_batched_cuda);
     m.impl("decompress", &decompress_cuda);
+    m.impl("multiply_ex", &multiply_ex_cuda);
     m.impl("multiply_frozen", &multiply_frozen_cuda);
     m.impl("plan_build", &plan_build_cuda);
     m.impl("multiply_planned", &multiply_planned_cuda);

@@ -120,11 +120,14 @@ class RowShardedMackoLinear(nn.Module):
         self.out_features, self.in_features = int(total_rows), int(cols)
         self.peer = peer
         self.shard = sharded.RowShard((values, deltas, row_indices, rows, cols), lo, hi, total_rows, blocks, peer.group)
+        torch.cuda.synchronize(values.device)   # the compressor has finished: the block is final from here on
+        self._c0_ptr = values.data_ptr()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.dim() != 1 or x.shape[0] != self.in_features:
             raise RuntimeError(f"expected a vector of {self.in_features} elements, got {tuple(x.shape)}")
-        return self.peer.multiply(self.shard, x.contiguous())
+        final = self.c_0.data_ptr() == self._c0_ptr   # buffers replaced since construction: no early matrix loads
+        return self.peer.multiply(self.shard, x.contiguous(), immutable=final)
 
 
 def compress_state_dict(state_dict, select=lambda name: ("self_attn" in name or "mlp" in name) and name.endswith(".weight")):

@@ -50,7 +50,7 @@ def _pruned_linear(out_features: int, in_features: int, density: float, seed: in
         with torch.no_grad():
             lin.weight.copy_(w)
         return lin
-    return MackoLinear(compress(w))
+    return MackoLinear(compress(w)).freeze()   # weights are final: see MackoLinear.freeze
 
 
 class RMSNorm(nn.Module):
@@ -244,7 +244,6 @@ def main():
         from .sharded import PeerGather
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.pop("NCCL_DEBUG", None)
         dist.init_process_group("nccl", device_id=device)
         cfg = LLAMA2_7B
         peer = PeerGather(max(3 * cfg["hidden"], 2 * cfg["ffn"], cfg["vocab"]), device)
@@ -282,12 +281,12 @@ def main():
             "cuda_graph": not args.no_graph, "batched_prefill": bool(args.batched_prefill), "first_tokens": tokens[:8].tolist(),
         }), flush=True)
     if world > 1:
-        # leave without tearing the communicator down while a captured graph still references it
+        # in order: the model (its layers hold the exchange buffers), the buffers, then the process group
         torch.cuda.synchronize()
         dist.barrier()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
+        del model
+        peer.close()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -191,13 +191,14 @@ class PeerGather:
             comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
             x.data_ptr(), table, shard.row_lo, self._flag_table, self.rank, self.world, flags, self.spin_limit, stream))
 
-    def multiply(self, shard: RowShard, x: torch.Tensor) -> torch.Tensor:
-        """Full y (a view of the current slot, length shard.total_rows) after all ranks delivered."""
+    def multiply(self, shard: RowShard, x: torch.Tensor, immutable: bool = False) -> torch.Tensor:
+        """Full y (a view of the current slot, length shard.total_rows) after all ranks delivered.
+        `immutable`: the shard's buffers are final (weights), see MACKO_SPMV_MATRIX_IMMUTABLE."""
         if shard.total_rows > self.max_rows:
             raise ValueError(f"matrix has {shard.total_rows} rows, the exchange buffers hold {self.max_rows}")
         slot = self._slot
         self._slot ^= 1
-        self._launch(shard, x, self._table(slot, 0), 0)
+        self._launch(shard, x, self._table(slot, 0), self._cabi.SPMV_MATRIX_IMMUTABLE if immutable else 0)
         # the kernel itself returns only after the slices of all ranks have landed (its last CTA waits)
         return self.buf[slot, : shard.total_rows]
 

@@ -172,6 +172,8 @@ def test_planned_product_long_rows_among_short_ones(shape):
         _check_y(y, comp_np, xn, f"{shape} seg={seg}")
         again = _planned(lib, comp, plan, info, x, flags=cabi.SPMV_MATRIX_IMMUTABLE)
         assert torch.equal(y.view(torch.int16), again.view(torch.int16)), "segments must be summed in a fixed order"
+        torch.cuda.synchronize()
+        assert not plan[32:40].any(), "the hand-out counters of the plan must be back at zero after a launch"
     # alpha / beta through the plan (cut rows read y once, when their last segment arrives)
     y0 = torch.ones(rows, dtype=torch.float16, device="cuda")
     _planned(lib, comp, plan, info, x, y=y0, alpha=0.5, beta=2.0)
