@@ -890,7 +890,7 @@ def run_own_arm(args):
         del graphs
         graphs = None
         dens = (0.5, 0.1, 1.0) if world == 1 else (0.5, 0.1)
-        cfg_rows = max(3 * 4096, 2 * 11008, 32000)
+        cfg_rows = max(world * 4096, 32000)   # N partial hidden vectors of a column-sharded layer, or the logits
         decode = decode_leg(device, world, lambda: sharded.PeerGather(cfg_rows, device), dens, args.decode_layers,
                             args.decode_prompt, args.decode_tokens)
 

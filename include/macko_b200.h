@@ -123,12 +123,12 @@ int macko_spmv_shape(int64_t rows, int64_t cols, int64_t padded_count, int sm_co
  * Planned launch, for matrices whose rows are very long or very uneven. A plan is side metadata built once
  * per matrix on the GPU from row_indices and deltas; the three MACKO buffers are not modified and stay what
  * the reference format defines. It cuts every row into virtual rows of at most `segment_elements` stored
- * elements (0 = default 1024; a multiple of 256, at most 3840), records for each where the decode has to
+ * elements (0 = default 1536; a multiple of 256, at most 3840), records for each where the decode has to
  * resume (the column sum in front of the segment), sorts them by length and deals them to the warps longest
- * first, so that every warp gets the same number of stored elements whatever the row lengths are. The
- * segments of a cut row leave fp32 partial sums inside the plan; the segment that finishes last adds them up
- * in segment order, so y is reproducible from call to call. Results match macko_spmv_fp16 up to the order of
- * the fp32 additions.
+ * first, so that every warp gets about the same number of stored elements whatever the row lengths are. The
+ * segments of a cut row leave fp32 partial sums inside the plan; a second, tiny kernel enqueued right behind
+ * the product adds them up in segment order, so y is reproducible from call to call. Results match
+ * macko_spmv_fp16 up to the order of the fp32 additions.
  *
  *   macko_spmv_plan_bytes  size of the plan buffer for a matrix (-1 for arguments a plan cannot index)
  *   macko_spmv_plan        builds the plan into `plan` (device memory, 16-byte aligned) and fills `info`

@@ -92,7 +92,7 @@ def _multiply_frozen_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, V):
 
 
 @torch.library.register_fake("macko_spmv::multiply_planned")
-def _multiply_planned_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, plan, virtual_rows, segment_elements, V, frozen):
+def _multiply_planned_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, plan, virtual_rows, segment_elements, split_rows, V, frozen):
     return torch.empty((M_rows,), device=M_values.device, dtype=M_values.dtype)
 
 
@@ -184,7 +184,7 @@ def multiply(compressed_M, V, out=None):
         if compressed_M.plan is not None:
             return torch.ops.macko_spmv.multiply_planned.default(
                 compressed_M[0], compressed_M[1], compressed_M[2], compressed_M[3], compressed_M[4],
-                compressed_M.plan, compressed_M.plan_meta[0], compressed_M.plan_meta[1], V, True)
+                compressed_M.plan, compressed_M.plan_meta[0], compressed_M.plan_meta[1], compressed_M.plan_meta[3], V, True)
         return torch.ops.macko_spmv.multiply_frozen.default(
             compressed_M[0], compressed_M[1], compressed_M[2], compressed_M[3], compressed_M[4], V)
     return torch.ops.macko_spmv.multiply.default(

@@ -34,7 +34,8 @@ plan_count_kernel(const int *__restrict__ ri, int rows, int stored, int seg, int
 __global__ void __launch_bounds__(256)
 plan_segments_kernel(const unsigned *__restrict__ deltas32, const int *__restrict__ ri, int rows, int stored, int seg,
                      const int *__restrict__ seg_first, int *__restrict__ tmp_begin, unsigned *__restrict__ tmp_pk,
-                     unsigned *__restrict__ tmp_out, unsigned *__restrict__ vrow)
+                     unsigned *__restrict__ tmp_out, unsigned *__restrict__ vrow, unsigned *__restrict__ split_list,
+                     unsigned *__restrict__ header)
 {
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -52,6 +53,7 @@ plan_segments_kernel(const unsigned *__restrict__ deltas32, const int *__restric
         }
         return;
     }
+    if (lane == 0) split_list[atomicAdd(header + 3, 1u)] = (unsigned)row;   // the rows the combining pass has to visit
     const int a0 = b & ~7;
     unsigned running = 0;   // sum of (delta + 1) over the row's elements in front of the current step
     for (int base = a0; base < e; base += 256) {
@@ -209,7 +211,7 @@ int macko_spmv_plan(const void *deltas, const int32_t *row_indices, int64_t rows
     char *base = static_cast<char *>(plan);
     unsigned *header = reinterpret_cast<unsigned *>(base + lay.header);
     int *seg_first = reinterpret_cast<int *>(base + lay.seg_first);
-    unsigned *arrived = reinterpret_cast<unsigned *>(base + lay.arrived);
+    unsigned *split_list = reinterpret_cast<unsigned *>(base + lay.split_list);
     uint2 *desc = reinterpret_cast<uint2 *>(base + lay.desc);
     unsigned *out = reinterpret_cast<unsigned *>(base + lay.out);
     unsigned *vrow = reinterpret_cast<unsigned *>(base + lay.vrow);
@@ -221,7 +223,6 @@ int macko_spmv_plan(const void *deltas, const int32_t *row_indices, int64_t rows
     const int r = (int)rows, stored = (int)padded_count;
 
     cudaError_t e = cudaMemsetAsync(header, 0, 64, s);
-    if (e == cudaSuccess) e = cudaMemsetAsync(arrived, 0, 4 * (size_t)(rows + 1), s);
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "plan memset: %s", cudaGetErrorString(e));
     if (rows > 0)
         plan_count_kernel<<<(r + 255) / 256, 256, 0, s>>>(row_indices, r, stored, seg, seg_first, header);
@@ -229,7 +230,7 @@ int macko_spmv_plan(const void *deltas, const int32_t *row_indices, int64_t rows
     if (st != MACKO_OK) return st;
     if (rows > 0)
         plan_segments_kernel<<<(r + 7) / 8, 256, 0, s>>>(static_cast<const unsigned *>(deltas), row_indices, r, stored, seg,
-                                                         seg_first, tmp_begin, tmp_pk, tmp_out, vrow);
+                                                         seg_first, tmp_begin, tmp_pk, tmp_out, vrow, split_list, header);
     plan_hist_kernel<<<blocks, 1024, 0, s>>>(seg_first, r, tmp_begin, tmp_pk, block_hist);
     plan_offsets_kernel<<<1, kPlanBuckets, 0, s>>>(block_hist, blocks, seg_first, r, header);
     plan_scatter_kernel<<<blocks, 1024, 0, s>>>(seg_first, r, tmp_begin, tmp_pk, tmp_out, block_hist, desc, out);

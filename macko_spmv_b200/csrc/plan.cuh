@@ -17,7 +17,7 @@ namespace macko {
 
 constexpr int kPlanLenBits = 12;                         // a virtual row holds fewer than 4096 stored elements
 constexpr int kPlanMaxSegment = 3840;                    // largest segment length (a multiple of 256)
-constexpr int kPlanDefaultSegment = 1024;
+constexpr int kPlanDefaultSegment = 1536;
 constexpr int kPlanBuckets = 64;                         // length classes: 64-element sub-steps spanned, 0..60
 constexpr unsigned kPlanPartialBit = 0x80000000u;        // destination word: a partial-sum slot, not a row of y
 
@@ -28,8 +28,8 @@ struct PlanView {
     const unsigned *vrow;   // natural order: row of each virtual row
     float *partial;         // natural order: fp32 sums of the segments of rows cut into several
     const int *seg_first;   // [rows + 1] natural index of the first virtual row of each row
-    unsigned *arrived;      // [rows] segments of the row whose partial sum is in; back to 0 when the row is written
-    unsigned *sched;        // [0] blocks handed out beyond every warp's first, [1] warps that have left; both 0 between launches
+    const unsigned *split_list;   // rows cut into several segments (in no particular order)
+    int n_split;
     int n_virtual;
 };
 
@@ -37,7 +37,7 @@ struct PlanView {
 // into segments of `seg` elements. Pure arithmetic, shared by the builder and the launcher.
 struct PlanLayout {
     long long v_max;        // upper bound of the number of virtual rows
-    long long header, seg_first, arrived, desc, out, vrow, partial, tmp_begin, tmp_pk, tmp_out, block_hist, total;
+    long long header, seg_first, split_list, desc, out, vrow, partial, tmp_begin, tmp_pk, tmp_out, block_hist, total;
 };
 
 inline PlanLayout plan_layout(long long rows, long long padded, int seg)
@@ -51,7 +51,7 @@ inline PlanLayout plan_layout(long long rows, long long padded, int seg)
     long long at = 0;
     l.header = at;      at = up(at + 64);
     l.seg_first = at;   at = up(at + 4 * (rows + 1));
-    l.arrived = at;     at = up(at + 4 * (rows + 1));
+    l.split_list = at;  at = up(at + 4 * (rows + 1));
     l.desc = at;        at = up(at + 8 * l.v_max);
     l.out = at;         at = up(at + 4 * l.v_max);
     l.vrow = at;        at = up(at + 4 * l.v_max);

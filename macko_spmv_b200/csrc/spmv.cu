@@ -36,6 +36,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace macko {
 namespace {
@@ -163,8 +164,8 @@ __device__ __forceinline__ void mask_unit(uint4 &v, unsigned &w, int lo, int hi)
 template <int V> struct Int { static constexpr int value = V; };
 
 // A virtual row of a planned launch is done (called by the leader lane of its group): a whole row goes to
-// y; a segment of a long row leaves its fp32 sum in the plan, and the segment that finds all others of its
-// row delivered adds them up in segment order, so the result does not depend on who finishes last.
+// y; a segment of a cut row leaves its fp32 sum in the plan, where plan_combine_kernel adds the segments of
+// every cut row in segment order once the product kernel has finished.
 __device__ __forceinline__ void plan_row_done(const PlanView &pl, unsigned o, float total, float alpha, float beta,
                                               unsigned short *__restrict__ y16, int rows)
 {
@@ -177,23 +178,27 @@ __device__ __forceinline__ void plan_row_done(const PlanView &pl, unsigned o, fl
         return;
     }
     const unsigned v = o & ~kPlanPartialBit;
-    if (v >= (unsigned)pl.n_virtual) return;
-    const unsigned row = __ldg(pl.vrow + v);
+    if (v < (unsigned)pl.n_virtual) pl.partial[v] = total;
+}
+
+// y[row] = fp16(alpha * (sum of the row's segment sums, in segment order) + beta * y[row]) for every cut row.
+// Launched right behind the product kernel of a planned launch, as its programmatic dependent.
+__global__ void __launch_bounds__(256)
+plan_combine_kernel(const PlanView pl, float alpha, float beta, unsigned short *__restrict__ y16, int rows)
+{
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= pl.n_split) return;
+    const unsigned row = __ldg(pl.split_list + i);
     if (row >= (unsigned)rows) return;
     const int first = __ldg(pl.seg_first + row);
-    const int n = __ldg(pl.seg_first + row + 1) - first;
-    __stcg(pl.partial + v, total);
-    __threadfence();   // the partial sum is visible device-wide before this segment counts as delivered
-    const unsigned before = atomicAdd(pl.arrived + row, 1u);
-    if ((int)before == n - 1) {
-        __threadfence();   // every segment counted before this one has its partial sum visible
-        float sum = 0.f;
-        for (int i = 0; i < n; ++i) sum += __ldcg(pl.partial + first + i);
-        float r = alpha * sum;
-        if (beta != 0.f) r += beta * __half2float(__ushort_as_half(y16[row]));
-        y16[row] = __half_as_ushort(__float2half_rn(r));
-        pl.arrived[row] = 0u;   // ready for the next launch with this plan
-    }
+    const int n = min(__ldg(pl.seg_first + row + 1), pl.n_virtual) - first;
+    float sum = 0.f;
+    for (int k = 0; k < n; ++k) sum += __ldcg(pl.partial + first + k);
+    float r = alpha * sum;
+    if (beta != 0.f) r += beta * __half2float(__ushort_as_half(y16[row]));
+    y16[row] = __half_as_ushort(__float2half_rn(r));
 }
 
 constexpr int kMaxPeers = 8;
@@ -207,6 +212,16 @@ struct Peers {
     unsigned spin_limit;          // polls of the arrival counters before the wait gives up
     int deferred;                 // publish and return: the caller enqueues macko_peer_wait where y is consumed
 };
+
+constexpr unsigned kDebugStageFirst = 0x100u;   // experiment: stage x before the first matrix loads (plain launches)
+constexpr unsigned kDebugPlainCopy = 0x200u;    // experiment: stage x with loads and stores instead of asynchronous copies
+
+// Kernel variants without a scatter epilogue / without a plan take an empty structure in place of the tables:
+// the parameter block of the plain product stays small.
+struct NoPeers {};
+struct NoPlan {};
+template <bool P> using PeersArg = std::conditional_t<P, Peers, NoPeers>;
+template <bool P> using PlanArg = std::conditional_t<P, PlanView, NoPlan>;
 
 // What a launch carries besides the reference's arguments.
 struct Extra {
@@ -230,7 +245,8 @@ template <int L, int NPAIR, bool XS, bool PEER, int BV = 1, bool PLAN = false, b
 __global__ void __launch_bounds__(kThreads, 2)
 spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
             const int *__restrict__ ri, const __half *__restrict__ x, __half *__restrict__ y,
-            int rows, int cols, int stored, float alpha, float beta, const Peers peers, int batch, const Extra extra)
+            int rows, int cols, int stored, float alpha, float beta, int batch, unsigned flags,
+            const PeersArg<PEER> peers, const PlanArg<PLAN> plan)
 {
     static_assert(BV == 1 || (XS && !PEER), "batched products gather from shared memory and have no scatter epilogue");
     static_assert(!PLAN || (XS && !PEER && BV == 1), "planned launches are built for the single-vector product with x in shared memory");
@@ -250,7 +266,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     // drain. Memory written by earlier kernels of the stream (x, y, and the matrix unless the caller has
     // declared it immutable) is not touched before griddepcontrol.wait. Both are no-ops for a plain launch.
     asm volatile("griddepcontrol.launch_dependents;");
-    const bool matrix_early = (extra.flags & MACKO_SPMV_MATRIX_IMMUTABLE) != 0u;
+    const bool matrix_early = (flags & MACKO_SPMV_MATRIX_IMMUTABLE) != 0u;
     if (!matrix_early) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- this warp's work: a contiguous row range dealt in blocks of K rows (so that the groups of a warp
@@ -258,33 +274,33 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     //      list, the direction alternating from round to round (longest first: the ends even out) ------------
     const long long n_warps = (long long)gridDim.x * kWarpsPerCta;
     const long long warp_id = (long long)blockIdx.x * kWarpsPerCta + (tid >> 5);
-    int row_next = 0, row_hi = 0;   // plain: rows [row_next, row_hi) of this warp
-    if constexpr (!PLAN) {
+    int row_next, row_hi;   // plain: rows [row_next, row_hi); planned: positions in the warp's sequence
+    if constexpr (PLAN) {
+        const int V = plan.n_virtual;
+        const int W = (int)n_warps, w = (int)warp_id;
+        const int nb = (V + K - 1) / K;                 // blocks of K virtual rows
+        const int full_rounds = nb / W;
+        const int rest = nb - full_rounds * W;           // blocks of the last, partly filled round
+        const int slot = (full_rounds & 1) ? W - 1 - w : w;
+        const int count = full_rounds + (slot < rest ? 1 : 0);
+        row_next = 0;
+        row_hi = count * K;
+        if (count > 0) {
+            const int last_round = count - 1;
+            const int last_blk = last_round * W + ((last_round & 1) ? W - 1 - w : w);
+            if (last_blk == nb - 1) row_hi -= nb * K - V;   // the very last block may hold fewer than K
+        }
+    } else {
         const long long n_blocks = ((long long)rows + K - 1) / K;
         row_next = (int)min((long long)rows, (n_blocks * warp_id / n_warps) * K);
         row_hi = (int)min((long long)rows, (n_blocks * (warp_id + 1) / n_warps) * K);
     }
-    // Planned: the sorted virtual rows are handed out in blocks of K (one per group, similar lengths), longest
-    // first. Block `warp_id` is this warp's first; every further block comes from a counter in the plan
-    // (atomicAdd), fetched one block ahead together with the block's descriptors, so that a warp never waits
-    // for either: longest-first with a shared counter keeps all warps busy until the short rows run out.
-    const int plan_blocks = PLAN ? (extra.plan.n_virtual + K - 1) / K : 0;
-    int nxt_blk = PLAN ? (int)min(warp_id, (long long)plan_blocks) : 0;   // block whose descriptors are in n_*
-    int nn_blk = plan_blocks;                                            // lane 0: the block after that (counter value)
-    int n_b = 0;            // descriptors of block nxt_blk for my group
-    unsigned n_pk = 0u, n_out = 0xffffffffu;
-    auto load_block = [&](int blk) {
-        const int v = blk * K + (lane / L);
-        n_b = 0; n_pk = 0u;
-        n_out = 0xffffffffu;   // no virtual row
-        if (blk < plan_blocks && v < extra.plan.n_virtual) {
-            const uint2 d = __ldg(extra.plan.desc + v);
-            n_b = (int)d.x;
-            n_pk = d.y;
-            n_out = __ldg(extra.plan.out + v);
-        }
+    // sorted index of position p of this warp's sequence (planned)
+    auto sorted_index = [&](int p) -> int {
+        const int W = (int)n_warps, w = (int)warp_id;
+        const int round = p / K;
+        return (round * W + ((round & 1) ? W - 1 - w : w)) * K + (p - round * K);
     };
-    if constexpr (PLAN) load_block(nxt_blk);
 
     // PEER: rows of the whole CTA (its warps own consecutive ranges) and the staging area for their y
     int cta_row_lo = 0, cta_row_hi = 0;
@@ -296,10 +312,22 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     }
     __half *ystage = reinterpret_cast<__half *>(smem + (((size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) + 15) & ~(size_t)15));
 
-    // Window of 32 row offsets held one per lane; entry r of the window is read by shuffle (plain launch).
+    // Window of 32 row offsets (planned: 32 virtual-row descriptors) held one per lane and read by shuffle.
     int win_base = row_next;
-    int ri_reg = 0;
-    if (!PLAN && row_next < row_hi) ri_reg = __ldg(ri + min(win_base + lane, rows));
+    int ri_reg = 0;      // plain: ri[win_base + lane]; planned: first stored element of the virtual row
+    unsigned pk_reg = 0; // planned: length | starting column << kPlanLenBits
+    auto load_window = [&]() {
+        if constexpr (PLAN) {
+            const int p = win_base + lane;
+            uint2 d = make_uint2(0u, 0u);
+            if (p < row_hi) d = __ldg(plan.desc + sorted_index(p));
+            ri_reg = (int)d.x;
+            pk_reg = d.y;
+        } else {
+            ri_reg = __ldg(ri + min(win_base + lane, rows));
+        }
+    };
+    if (row_next < row_hi) load_window();
 
     // ---- per-group state ------------------------------------------------------------------------------
     constexpr int LOG_STEP = (L == 32) ? 8 : (L == 16) ? 7 : (L == 8) ? 6 : 5;
@@ -322,8 +350,53 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
 #pragma unroll
     for (int b = 0; b < BV; ++b) accb[b][0] = accb[b][1] = 0.f;
 
+    // Stages x into shared memory, framed by zeros (one CTA-wide barrier at its end).
+    auto stage_x = [&]() {
+    if (BV > 1) {
+        __half *xs = reinterpret_cast<__half *>(smem);
+        const int n_total = (kXPadFront + cols + kXPadBack) * BV;
+#pragma unroll 1
+        for (int i = tid; i < kXPadFront * BV; i += kThreads) xs[i] = __ushort_as_half(0);
+#pragma unroll 1
+        for (int i = (kXPadFront + cols) * BV + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
+#pragma unroll
+        for (int b = 0; b < BV; ++b) {
+            const __half *xb = x + (size_t)b * cols;
+#pragma unroll 1
+            for (int c = tid; c < cols; c += kThreads)
+                xs[(size_t)(kXPadFront + c) * BV + b] = b < batch ? xb[c] : __ushort_as_half(0);
+        }
+        __syncthreads();
+    } else if (XS) {
+        __half *xs = reinterpret_cast<__half *>(smem);
+        const int n_total = kXPadFront + cols + kXPadBack;
+#pragma unroll 1
+        for (int i = tid; i < kXPadFront; i += kThreads) xs[i] = __ushort_as_half(0);
+#pragma unroll 1
+        for (int i = kXPadFront + cols + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
+        if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            // 16-byte asynchronous copies global -> shared: no registers, all of a thread's copies in flight
+            // together, and the matrix loads issued above stay in flight beside them
+            const int n_vec = cols >> 3;
+            const unsigned dst0 = (unsigned)x_base + 2u * kXPadFront;
+            const char *src0 = reinterpret_cast<const char *>(x);
+#pragma unroll 1
+            for (int i = tid; i < n_vec; i += kThreads)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + 16u * (unsigned)i), "l"(src0 + 16 * (size_t)i) : "memory");
+#pragma unroll 1
+            for (int i = (n_vec << 3) + tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        } else {
+#pragma unroll 1
+            for (int i = tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
+        }
+        __syncthreads();
+    }
+    };
+    const bool stage_first = (flags & kDebugStageFirst) != 0u && !matrix_early;
+    if (stage_first) stage_x();
     bool first_pass = true;
-    bool plan_first = PLAN;
     for (;;) {
         bool done = false;
         // ---- groups that ran out of work finish their row and take the next one ---------------------
@@ -337,7 +410,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 if (need) {
                     if (my_row >= 0 && lig == 0) {
                         if constexpr (PLAN) {
-                            plan_row_done(extra.plan, out_word, total, alpha, beta, y16, rows);
+                            plan_row_done(plan, out_word, total, alpha, beta, y16, rows);
                         } else if constexpr (PEER) {
                             ystage[my_row - cta_row_lo] = __float2half_rn(alpha * total);   // delivered in bulk at the end
                         } else {
@@ -365,61 +438,48 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                     }
                 }
             }
-            if constexpr (PLAN) {
-                if (needmask != 0xffffffffu) {
-                    // some group of the block is still at work: the others idle until the whole block is done
-                    if (need) { my_row = -1; pos = 0; end = 0; begin = 0; }
-                } else if (nxt_blk >= plan_blocks) {
-                    done = true;
-                    my_row = -1; pos = 0; end = 0; begin = 0;
-                } else {
-                    // adopt the block fetched ahead; offsets are clamped into [0, stored] so that a corrupt plan
-                    // cannot send loads outside values/deltas
-                    const int b = min(max(n_b, 0), stored);
-                    const int e = min(b + (int)(n_pk & ((1u << kPlanLenBits) - 1u)), stored);
-                    out_word = n_out;
-                    if (n_out == 0xffffffffu) {
-                        my_row = -1; pos = 0; end = 0; begin = 0;
-                    } else {
-                        my_row = 0;
-                        begin = b; end = e; pos = b & ~(kGroup - 1);
-                        run = lane_const + ((n_pk >> kPlanLenBits) << 1) - 2u * (unsigned)(b & (kGroup - 1));
-                    }
-                    // and fetch ahead again: the next block's descriptors, and the counter for the one after it
-                    if (!first_pass) {
-                        nxt_blk = __shfl_sync(0xffffffffu, nn_blk, 0);
-                        load_block(nxt_blk);
-                        if (lane == 0) nn_blk = (int)atomicAdd(extra.plan.sched, 1u) + (int)n_warps;
-                    }
-                }
+            const int avail = row_hi - row_next;
+            if (avail <= 0) {
+                if (needmask == 0xffffffffu) done = true;
+                if (need) { my_row = -1; pos = 0; end = 0; begin = 0; }
             } else {
-                const int avail = row_hi - row_next;
-                if (avail <= 0) {
-                    if (needmask == 0xffffffffu) done = true;
-                    if (need) { my_row = -1; pos = 0; end = 0; begin = 0; }
-                } else {
-                    const unsigned leaders = needmask & kLeaders;
-                    const int want = __popc(leaders);
-                    const int take = min(want, avail);
-                    if (row_next + take > win_base + 31) {  // warp-uniform
-                        win_base = row_next;
-                        ri_reg = __ldg(ri + min(win_base + lane, rows));
-                    }
-                    const int rank = __popc(leaders & ((1u << group_lane0) - 1u));
-                    const int nr = row_next + rank;
-                    // offsets are clamped into [0, stored] so that a corrupt row_indices cannot send loads outside values/deltas
-                    const int b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
-                    const int e = min(__shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31), stored);
-                    if (need) {
-                        if (rank < take) {
-                            my_row = nr; begin = b; end = e; pos = b & ~(kGroup - 1);
-                            run = lane_const - 2u * (unsigned)(b & (kGroup - 1));   // the unit that holds `begin` starts before the row
-                        } else {
-                            my_row = -1; pos = 0; end = 0; begin = 0;
-                        }
-                    }
-                    row_next += take;
+                const unsigned leaders = needmask & kLeaders;
+                const int want = __popc(leaders);
+                const int take = min(want, avail);
+                if (row_next + take > win_base + (PLAN ? 32 : 31)) {  // warp-uniform
+                    win_base = row_next;
+                    load_window();
                 }
+                const int rank = __popc(leaders & ((1u << group_lane0) - 1u));
+                const int nr = row_next + rank;
+                // offsets are clamped into [0, stored] so that corrupt row_indices (or a corrupt plan) cannot send
+                // loads outside values/deltas
+                int b, e;
+                unsigned colbase2 = 0u;   // planned: twice the column sum in front of the segment (a byte offset into x)
+                if constexpr (PLAN) {
+                    b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
+                    const unsigned pk = __shfl_sync(0xffffffffu, pk_reg, (nr - win_base) & 31);
+                    e = min(b + (int)(pk & ((1u << kPlanLenBits) - 1u)), stored);
+                    colbase2 = (pk >> kPlanLenBits) << 1;
+                } else {
+                    b = min(max(__shfl_sync(0xffffffffu, ri_reg, (nr - win_base) & 31), 0), stored);
+                    e = min(__shfl_sync(0xffffffffu, ri_reg, (nr + 1 - win_base) & 31), stored);
+                }
+                if (need) {
+                    if (rank < take) {
+                        if constexpr (PLAN) {
+                            my_row = 0;
+                            out_word = __ldg(plan.out + sorted_index(nr));   // needed only when the virtual row ends
+                        } else {
+                            my_row = nr;
+                        }
+                        begin = b; end = e; pos = b & ~(kGroup - 1);
+                        run = lane_const + colbase2 - 2u * (unsigned)(b & (kGroup - 1));   // the unit that holds `begin` starts before the row
+                    } else {
+                        my_row = -1; pos = 0; end = 0; begin = 0;
+                    }
+                }
+                row_next += take;
             }
         }
 
@@ -449,60 +509,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         if (first_pass) {
             first_pass = false;
             if (matrix_early) asm volatile("griddepcontrol.wait;" ::: "memory");
-            if (BV > 1) {
-                __half *xs = reinterpret_cast<__half *>(smem);
-                const int n_total = (kXPadFront + cols + kXPadBack) * BV;
-#pragma unroll 1
-                for (int i = tid; i < kXPadFront * BV; i += kThreads) xs[i] = __ushort_as_half(0);
-#pragma unroll 1
-                for (int i = (kXPadFront + cols) * BV + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
-#pragma unroll
-                for (int b = 0; b < BV; ++b) {
-                    const __half *xb = x + (size_t)b * cols;
-#pragma unroll 1
-                    for (int c = tid; c < cols; c += kThreads)
-                        xs[(size_t)(kXPadFront + c) * BV + b] = b < batch ? xb[c] : __ushort_as_half(0);
-                }
-                __syncthreads();
-            } else if (XS) {
-                __half *xs = reinterpret_cast<__half *>(smem);
-                const int n_total = kXPadFront + cols + kXPadBack;
-#pragma unroll 1
-                for (int i = tid; i < kXPadFront; i += kThreads) xs[i] = __ushort_as_half(0);
-#pragma unroll 1
-                for (int i = kXPadFront + cols + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
-                if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-                    // 16-byte asynchronous copies global -> shared: no registers, all of a thread's copies in flight
-                    // together, and the matrix loads issued above stay in flight beside them
-                    const int n_vec = cols >> 3;
-                    const unsigned dst0 = (unsigned)x_base + 2u * kXPadFront;
-                    const char *src0 = reinterpret_cast<const char *>(x);
-#pragma unroll 1
-                    for (int i = tid; i < n_vec; i += kThreads)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + 16u * (unsigned)i), "l"(src0 + 16 * (size_t)i) : "memory");
-#pragma unroll 1
-                    for (int i = (n_vec << 3) + tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
-                    asm volatile("cp.async.commit_group;" ::: "memory");
-                    asm volatile("cp.async.wait_group 0;" ::: "memory");
-                } else {
-#pragma unroll 1
-                    for (int i = tid; i < cols; i += kThreads) xs[kXPadFront + i] = x[i];
-                }
-                __syncthreads();
-            }
-        }
-        if constexpr (PLAN) {
-            if (plan_first) {
-                // The counter belongs to the plan, which the previous kernel of the stream may have been using: it
-                // is first touched here, behind the wait. Two values: the block after this warp's first one (its
-                // descriptors are loaded now, consumed at the next hand-over) and the one after that.
-                plan_first = false;
-                unsigned a0 = 0u;
-                if (lane == 0) a0 = atomicAdd(extra.plan.sched, 1u);
-                nxt_blk = (int)__shfl_sync(0xffffffffu, a0, 0) + (int)n_warps;
-                load_block(nxt_blk);
-                if (lane == 0) nn_blk = (int)atomicAdd(extra.plan.sched, 1u) + (int)n_warps;
-            }
+            if (!stage_first) stage_x();
         }
         if (done) break;
 
@@ -618,20 +625,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         pos += D * STEP;
     }
 
-    if constexpr (PLAN) {
-        // The warp that leaves last puts the plan's counters back to zero for the next launch. The fence orders
-        // this warp's last counter update (a value it never used may still be on its way) before its sign-off.
-        if (lane == 0) {
-            __threadfence();
-            const unsigned left = atomicAdd(extra.plan.sched + 1, 1u);
-            if (left == (unsigned)n_warps - 1u) {
-                extra.plan.sched[0] = 0u;
-                extra.plan.sched[1] = 0u;
-            }
-        }
-    }
-
-    if (PEER) {
+    if constexpr (PEER) {
         // Every CTA writes the y values of its (contiguous) rows into this rank's own copy of the full y with
         // coalesced stores, makes them visible on this GPU and takes a ticket. The CTA that takes the last
         // ticket then forwards the rank's whole slice to the other ranks over NVLink and publishes it with one
@@ -778,9 +772,14 @@ int launch(const void *values, const void *deltas, const int32_t *ri, int rows, 
     // next kernel move in early only takes SM slots away from it (measured: slower). With a deferred wait the
     // kernel publishes and returns, and overlaps like any other.
     cfg.numAttrs = (use_pdl() && (!PEER || peers.deferred)) ? 1 : 0;
+    PeersArg<PEER> peers_arg{};
+    PlanArg<PLAN> plan_arg{};
+    if constexpr (PEER) peers_arg = peers;
+    if constexpr (PLAN) plan_arg = extra.plan;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel,
         static_cast<const uint4 *>(values), static_cast<const unsigned *>(deltas), ri,
-        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta, peers, batch, extra);
+        static_cast<const __half *>(x), static_cast<__half *>(y), rows, cols, (int)padded, alpha, beta, batch, extra.flags,
+        peers_arg, plan_arg);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "spmv launch: %s", cudaGetErrorString(e));
     return MACKO_OK;
@@ -887,6 +886,15 @@ int check_args(const void *values, const void *deltas, const int32_t *ri, int64_
 namespace macko {
 namespace {
 
+unsigned debug_flags()
+{
+    static const unsigned bits = [] {
+        const char *v = getenv("MACKO_SPMV_DEBUG");
+        return v ? (unsigned)strtoul(v, nullptr, 0) & 0x300u : 0u;
+    }();
+    return bits;
+}
+
 int check_flags(uint32_t flags)
 {
     if (flags & ~(uint32_t)MACKO_SPMV_MATRIX_IMMUTABLE)
@@ -915,7 +923,7 @@ int spmv_default(const void *values, const void *deltas, const int32_t *row_indi
     const bool xs = smem <= (size_t)dev->max_smem_optin;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     Extra extra = {};
-    extra.flags = flags;
+    extra.flags = flags | debug_flags();
     if (xs)
         return launch_l<true, BF>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
     return launch_l<false, BF>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
@@ -1006,12 +1014,29 @@ int macko_spmv_fp16_planned(const void *values, const void *deltas, const int32_
     extra.plan.vrow = reinterpret_cast<const unsigned *>(base + lay.vrow);
     extra.plan.partial = reinterpret_cast<float *>(base + lay.partial);
     extra.plan.seg_first = reinterpret_cast<const int *>(base + lay.seg_first);
-    extra.plan.arrived = reinterpret_cast<unsigned *>(base + lay.arrived);
-    extra.plan.sched = reinterpret_cast<unsigned *>(base + lay.header) + 8;
+    extra.plan.split_list = reinterpret_cast<const unsigned *>(base + lay.split_list);
+    extra.plan.n_split = info->split_rows;
     extra.plan.n_virtual = info->virtual_rows;
+    if (info->split_rows < 0 || info->split_rows > rows)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "the plan info is inconsistent (%d cut rows of %lld)", info->split_rows, (long long)rows);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return launch<8, 3, true, false, 1, true>(values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y,
-                                              alpha, beta, s, *dev, 0, Peers{}, 1, extra);
+    st = launch<8, 3, true, false, 1, true>(values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y,
+                                            alpha, beta, s, *dev, 0, Peers{}, 1, extra);
+    if (st != MACKO_OK || info->split_rows == 0) return st;
+    // the segments of the cut rows are added up by a second, tiny kernel that starts when the first has finished
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((info->split_rows + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, plan_combine_kernel, extra.plan, alpha, beta, static_cast<unsigned short *>(y), (int)rows);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "plan combine launch: %s", cudaGetErrorString(e));
+    return MACKO_OK;
 }
 
 int macko_spmv_shape(int64_t rows, int64_t cols, int64_t padded_count, int sm_count,

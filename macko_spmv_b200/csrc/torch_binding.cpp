@@ -106,7 +106,7 @@ std::tuple<at::Tensor, at::Tensor> plan_build_cuda(const at::Tensor &deltas, con
 
 at::Tensor multiply_planned_cuda(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
                                  int64_t rows, int64_t cols, const at::Tensor &plan, int64_t virtual_rows,
-                                 int64_t segment_elements, const at::Tensor &V, bool frozen)
+                                 int64_t segment_elements, int64_t split_rows, const at::Tensor &V, bool frozen)
 {
     check_compressed(values, deltas, ri, rows, cols);
     TORCH_CHECK(values.dtype() == at::kHalf && V.dtype() == at::kHalf, "the planned product is built for torch.half");
@@ -121,6 +121,7 @@ at::Tensor multiply_planned_cuda(const at::Tensor &values, const at::Tensor &del
     info.padded_count = values.numel();
     info.virtual_rows = (int32_t)virtual_rows;
     info.segment_elements = (int32_t)segment_elements;
+    info.split_rows = (int32_t)split_rows;
     const c10::cuda::CUDAGuard guard(values.device());
     at::Tensor y = at::empty({rows}, values.options());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
@@ -251,7 +252,7 @@ TORCH_LIBRARY(macko_spmv, m)
     m.def("multiply_frozen(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor V) -> Tensor");
     m.def("plan_build(Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, int padded_count, int segment_elements) -> (Tensor, Tensor)");
     m.def("multiply_planned(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor plan, "
-          "int virtual_rows, int segment_elements, Tensor V, bool frozen) -> Tensor");
+          "int virtual_rows, int segment_elements, int split_rows, Tensor V, bool frozen) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)

@@ -98,16 +98,21 @@ class RowShardedMackoLinear(nn.Module):
     """Tensor-parallel `MackoLinear`: this rank holds a contiguous block of output features (rows of W)
     in MACKO form; `forward` returns the full output on every rank.
 
-    The product and the exchange are one kernel (`sharded.PeerGather`). The returned tensor is a view of
-    one of the exchange's two slots: it must be consumed (in stream order) before the second-next
-    product issued through the same `PeerGather`; the decode loop in `llama_decode` does exactly that.
+    The product and the exchange are one kernel (`sharded.PeerGather`). With `copy_result=False` the returned
+    tensor is a view of one of the exchange's slots: it must be consumed (in stream order) before the
+    second-next product issued through the same `PeerGather`; the decode loop in `llama_decode` does exactly that.
     The reference has no multi-GPU layer; this is the layer its `fix()` would install under tensor
     parallelism."""
 
-    def __init__(self, weight_block: torch.Tensor, row_lo: int, total_rows: int, peer):
+    def __init__(self, weight_block: torch.Tensor, row_lo: int, total_rows: int, peer, slot: int | None = None,
+                 copy_result: bool = True):
         super().__init__()
         from . import compress, sharded
 
+        self.slot = slot   # exchange slot of this layer's product (None: the alternating pair), see sharded.PeerGather
+        # True: forward returns a tensor of its own. False: a view of the exchange slot, overwritten by the
+        # second-next product through the same PeerGather (for callers that consume it at once, like the decode loop)
+        self.copy_result = copy_result
         world = peer.world
         blocks = [sharded.row_block(total_rows, r, world) for r in range(world)]
         lo, hi = blocks[peer.rank]
@@ -127,7 +132,45 @@ class RowShardedMackoLinear(nn.Module):
         if x.dim() != 1 or x.shape[0] != self.in_features:
             raise RuntimeError(f"expected a vector of {self.in_features} elements, got {tuple(x.shape)}")
         final = self.c_0.data_ptr() == self._c0_ptr   # buffers replaced since construction: no early matrix loads
-        return self.peer.multiply(self.shard, x.contiguous(), immutable=final)
+        y = self.peer.multiply(self.shard, x.contiguous(), immutable=final, slot=self.slot)
+        return y.clone() if self.copy_result else y
+
+
+class ColumnShardedMackoLinear(nn.Module):
+    """Tensor-parallel `MackoLinear` split by input features: this rank holds the columns
+    [col_lo, col_lo + in_local) of W (all rows) in MACKO form and multiplies them with its slice of x; the
+    partial results of all ranks are added. `forward(x_local)` returns the full output on every rank.
+
+    Used where the input is already split (the attention output of a rank's heads, its slice of the MLP
+    activation): no gather of x is needed, one exchange per layer. The exchange is the fused one of
+    `sharded.PeerGather`: every rank's kernel stores its partial y into slot `rank` of an [N, out] buffer on
+    all ranks (the buffer is addressed as one y of N * out rows of which this rank owns rows
+    [rank * out, (rank + 1) * out)), and the N partial vectors are summed in rank order in fp32, so all ranks
+    get the same bits. The reference has no multi-GPU layer."""
+
+    def __init__(self, weight_columns: torch.Tensor, peer):
+        super().__init__()
+        from . import compress, sharded
+
+        world, rank = peer.world, peer.rank
+        values, deltas, row_indices, rows, cols = compress(weight_columns.contiguous())
+        self.register_buffer("c_0", values)
+        self.register_buffer("c_1", deltas)
+        self.register_buffer("c_2", row_indices)
+        self.out_features, self.in_local = int(rows), int(cols)
+        self.peer = peer
+        blocks = [(r * rows, (r + 1) * rows) for r in range(world)]
+        self.shard = sharded.RowShard((values, deltas, row_indices, rows, cols), rank * rows, (rank + 1) * rows,
+                                      world * rows, blocks, peer.group)
+        torch.cuda.synchronize(values.device)   # the compressor has finished: the block is final from here on
+        self._c0_ptr = values.data_ptr()
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        if x_local.dim() != 1 or x_local.shape[0] != self.in_local:
+            raise RuntimeError(f"expected this rank's {self.in_local} input features, got {tuple(x_local.shape)}")
+        final = self.c_0.data_ptr() == self._c0_ptr
+        parts = self.peer.multiply(self.shard, x_local.contiguous(), immutable=final)
+        return parts.view(self.peer.world, self.out_features).sum(dim=0, dtype=torch.float32).to(torch.float16)
 
 
 def compress_state_dict(state_dict, select=lambda name: ("self_attn" in name or "mlp" in name) and name.endswith(".weight")):

@@ -11,11 +11,13 @@ same single-token step. It is a caller of the hot path, used to report tokens/s;
     python -m macko_spmv_b200.llama_decode --density 0.5 --layers 32
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m macko_spmv_b200.llama_decode --density 0.5
 
-Tensor parallel (one process per GPU): every linear layer is split by output features into contiguous
-row blocks; each SpMV kernel stores its slice of y into every rank's copy over NVLink and ends when all
-slices have arrived (`RowShardedMackoLinear`), so a token costs 4 fused product+exchange kernels per
-block and no collective call. Norms, rotary embedding, the KV cache and attention are replicated: at
-batch 1 attention over a few hundred positions takes microseconds, less than one more exchange would.
+Tensor parallel (one process per GPU): the attention heads are split over the ranks. A rank holds the rows
+of the q/k/v projection that belong to its heads and the matching rows of gate/up (plain local products, no
+exchange: their input is the replicated hidden state), its heads' slice of the KV cache, and the columns of
+the o and down projections that its slice of the attention output / MLP activation feeds
+(`ColumnShardedMackoLinear`: partial products of all ranks are exchanged by the SpMV kernel itself and added).
+A token therefore costs two fused product+exchange kernels per block plus one for the row-sharded LM head
+(`RowShardedMackoLinear`), and no collective call; norms and rotary embedding are replicated.
 """
 from __future__ import annotations
 
@@ -29,12 +31,37 @@ import torch
 from torch import nn
 
 from . import compress, workloads
-from .linear import MackoLinear, RowShardedMackoLinear
+from .linear import ColumnShardedMackoLinear, MackoLinear, RowShardedMackoLinear
 
 LLAMA2_7B = dict(hidden=4096, heads=32, ffn=11008, vocab=32000, layers=32, eps=1e-5, rope_theta=10000.0)
 
 
-def _pruned_linear(out_features: int, in_features: int, density: float, seed: int, device, peer=None) -> nn.Module:
+def _local_rows(w: torch.Tensor, parts: int, rank: int, world: int) -> torch.Tensor:
+    """Rows of `w` = `parts` matrices stacked (q/k/v or gate/up): this rank's block of each part, stacked again."""
+    n = w.shape[0] // parts
+    if n % world:
+        raise ValueError(f"{n} output features do not split over {world} ranks")
+    b = n // world
+    return torch.cat([w[p * n + rank * b: p * n + (rank + 1) * b] for p in range(parts)], dim=0).contiguous()
+
+
+def _tp_linear(out_features: int, in_features: int, density: float, seed: int, device, peer, split: str, parts: int = 1):
+    """One rank's share of a pruned linear layer under tensor parallelism. The full matrix is generated and
+    pruned per row exactly as on one GPU, then cut: split="rows" keeps this rank's output features (of each of
+    the `parts` stacked matrices) as a local MackoLinear; split="cols" keeps its input features as a
+    ColumnShardedMackoLinear whose partial products are exchanged and added."""
+    if density >= 1.0:
+        raise ValueError("the tensor-parallel path runs MACKO layers only (density < 1)")
+    w = workloads.magnitude_pruned_matrix(out_features, in_features, density, seed, device=device)
+    if split == "rows":
+        return MackoLinear(compress(_local_rows(w, parts, peer.rank, peer.world))).freeze()
+    if in_features % peer.world:
+        raise ValueError(f"{in_features} input features do not split over {peer.world} ranks")
+    b = in_features // peer.world
+    return ColumnShardedMackoLinear(w[:, peer.rank * b:(peer.rank + 1) * b], peer)
+
+
+def _pruned_linear(out_features: int, in_features: int, density: float, seed: int, device, peer=None, slot=None) -> nn.Module:
     """A MackoLinear (density < 1) or a dense nn.Linear (density >= 1, the cuBLAS baseline); with `peer`
     (a `sharded.PeerGather`) this rank's row block as a RowShardedMackoLinear."""
     w = workloads.magnitude_pruned_matrix(out_features, in_features, min(density, 1.0), seed, device=device)
@@ -44,7 +71,7 @@ def _pruned_linear(out_features: int, in_features: int, density: float, seed: in
         from .sharded import row_block
 
         lo, hi = row_block(out_features, peer.rank, peer.world)
-        return RowShardedMackoLinear(w[lo:hi], lo, out_features, peer)
+        return RowShardedMackoLinear(w[lo:hi], lo, out_features, peer, slot=slot, copy_result=False)   # consumed at once
     if density >= 1.0:
         lin = nn.Linear(in_features, out_features, bias=False, device=device, dtype=torch.float16)
         with torch.no_grad():
@@ -71,13 +98,22 @@ class Block(nn.Module):
     def __init__(self, cfg, density, seed, device, max_len, peer=None):
         super().__init__()
         h, f = cfg["hidden"], cfg["ffn"]
-        self.heads = cfg["heads"]
-        self.head_dim = h // self.heads
-        self.hidden, self.ffn = h, f
-        self.qkv_proj = _pruned_linear(3 * h, h, density, seed + 0, device, peer)
-        self.o_proj = _pruned_linear(h, h, density, seed + 3, device, peer)
-        self.gate_up_proj = _pruned_linear(2 * f, h, density, seed + 4, device, peer)
-        self.down_proj = _pruned_linear(h, f, density, seed + 6, device, peer)
+        world = peer.world if peer is not None else 1
+        if cfg["heads"] % world or f % world:
+            raise ValueError(f"{cfg['heads']} heads / {f} MLP features do not split over {world} ranks")
+        self.head_dim = h // cfg["heads"]
+        self.heads = cfg["heads"] // world          # heads held by this rank
+        self.hidden, self.ffn = h, f // world       # ffn: this rank's share of the MLP width
+        if peer is None:
+            self.qkv_proj = _pruned_linear(3 * h, h, density, seed + 0, device)
+            self.o_proj = _pruned_linear(h, h, density, seed + 3, device)
+            self.gate_up_proj = _pruned_linear(2 * f, h, density, seed + 4, device)
+            self.down_proj = _pruned_linear(h, f, density, seed + 6, device)
+        else:
+            self.qkv_proj = _tp_linear(3 * h, h, density, seed + 0, device, peer, "rows", parts=3)
+            self.o_proj = _tp_linear(h, h, density, seed + 3, device, peer, "cols")
+            self.gate_up_proj = _tp_linear(2 * f, h, density, seed + 4, device, peer, "rows", parts=2)
+            self.down_proj = _tp_linear(h, f, density, seed + 6, device, peer, "cols")
         self.input_norm = RMSNorm(h, cfg["eps"], device)
         self.post_norm = RMSNorm(h, cfg["eps"], device)
         self.register_buffer("k_cache", torch.zeros(1, self.heads, max_len, self.head_dim, dtype=torch.float16, device=device))
@@ -132,8 +168,10 @@ class LlamaDecoder(nn.Module):
         self.embed = (0.02 * torch.randn(cfg["vocab"], h, generator=g, device=device)).to(torch.float16)
         self.blocks = nn.ModuleList([Block(cfg, density, seed + 100 * (i + 1), device, max_len, peer) for i in range(cfg["layers"])])
         self.norm = RMSNorm(h, cfg["eps"], device)
+        # A decode step is two exchanges per block plus this one: an odd number. Replayed as one captured graph,
+        # its last exchange would be followed by its first in the same slot; the LM head takes the spare slot.
         self.lm_head = _pruned_linear(cfg["vocab"], h, density if prune_lm_head else 1.0, seed + 7, device,
-                                      peer if prune_lm_head else None)
+                                      peer if prune_lm_head else None, slot=2)
         half = (h // cfg["heads"]) // 2
         inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(half, device=device, dtype=torch.float32) / half))
         ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
@@ -246,7 +284,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
         cfg = LLAMA2_7B
-        peer = PeerGather(max(3 * cfg["hidden"], 2 * cfg["ffn"], cfg["vocab"]), device)
+        peer = PeerGather(max(world * cfg["hidden"], cfg["vocab"]), device)   # N partial vectors of the column-sharded layers, or the logits
     t0 = time.perf_counter()
     model = LlamaDecoder(args.density, layers=args.layers, device=device, max_len=args.prompt + args.new_tokens,
                          prune_lm_head=not args.dense_lm_head, peer=peer)

@@ -128,7 +128,10 @@ class PeerGather:
     Two ways to use it:
 
     * `multiply(shard, x)`: the kernel ends only when the slices of all ranks have landed (its last CTA
-      waits, bounded). Two y slots alternate, so a result stays valid until the call after next.
+      waits, bounded). Two y slots alternate, so a result stays valid until the call after next. Two
+      consecutive calls must never use the same slot (a faster rank writes its slice of the next product while
+      a slower one may still read the previous y): a fixed sequence with an odd number of calls that is
+      replayed again and again (a captured decode step) gives one of its calls `slot=2`, the spare slot.
     * `begin_step()`, then any number of `multiply_deferred(shard, x)`, then `wait()`: every product
       publishes its slice and returns at once (it overlaps with the next product like an ordinary kernel);
       each gets its own region of the step's half of the buffer, and one bounded wait kernel at the end
@@ -159,7 +162,7 @@ class PeerGather:
         self.max_rows = int(max_rows)
         # rows of one deferred step (sum over its products, each rounded up to 8), at least one product
         self.step_rows = max(int(step_rows), (self.max_rows + 7) // 8 * 8)
-        self.buf = symm_mem.empty((2, self.step_rows), dtype=torch.float16, device=device)
+        self.buf = symm_mem.empty((3, self.step_rows), dtype=torch.float16, device=device)   # two alternating slots / halves + a spare
         self.handle = symm_mem.rendezvous(self.buf, group)
         pad = self.handle.get_signal_pad(self.rank)
         pad.zero_()
@@ -191,13 +194,17 @@ class PeerGather:
             comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
             x.data_ptr(), table, shard.row_lo, self._flag_table, self.rank, self.world, flags, self.spin_limit, stream))
 
-    def multiply(self, shard: RowShard, x: torch.Tensor, immutable: bool = False) -> torch.Tensor:
+    def multiply(self, shard: RowShard, x: torch.Tensor, immutable: bool = False, slot: int | None = None) -> torch.Tensor:
         """Full y (a view of the current slot, length shard.total_rows) after all ranks delivered.
-        `immutable`: the shard's buffers are final (weights), see MACKO_SPMV_MATRIX_IMMUTABLE."""
+        `immutable`: the shard's buffers are final (weights), see MACKO_SPMV_MATRIX_IMMUTABLE.
+        `slot`: None = the two alternating slots; 2 = the spare slot (see the class description)."""
         if shard.total_rows > self.max_rows:
             raise ValueError(f"matrix has {shard.total_rows} rows, the exchange buffers hold {self.max_rows}")
-        slot = self._slot
-        self._slot ^= 1
+        if slot is None:
+            slot = self._slot
+            self._slot ^= 1
+        elif slot not in (0, 1, 2):
+            raise ValueError("slot must be 0, 1 or 2")
         self._launch(shard, x, self._table(slot, 0), self._cabi.SPMV_MATRIX_IMMUTABLE if immutable else 0)
         # the kernel itself returns only after the slices of all ranks have landed (its last CTA waits)
         return self.buf[slot, : shard.total_rows]

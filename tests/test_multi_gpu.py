@@ -1,7 +1,9 @@
 """Row-sharded product with the exchange fused into the kernel (`sharded.PeerGather`), run as child
 processes, one per GPU: on a single GPU with world size 1 (the kernel's scatter epilogue, flags and
 bounded wait run against its own buffers) and, when the box has two GPUs, with world size 2 against the
-NCCL all-gather path and a dense fp32 product."""
+NCCL all-gather path and a dense fp32 product. NVLS is off in NCCL and the symmetric buffers are not bound
+to an NVLink multicast object (`PeerGather` switches that off); every rank leaves between steps, after
+dropping its buffers and the process group."""
 import os
 import socket
 
@@ -46,12 +48,57 @@ def _worker(rank, world, port, q):
                     ok, msg = False, f"rank {rank}: {rows}x{cols} rep {rep} rel {rel}"
         if pg.error_flag() != 0:
             ok, msg = False, f"rank {rank}: wait gave up on rank {pg.error_flag() - 1}"
+        # deferred steps: several products publish without waiting, one wait at the end; two steps in a row use
+        # the two halves of the buffers; the second pair of steps is replayed from CUDA graphs
+        mats = []
+        for i, (rows, cols, d) in enumerate([(4096, 1024, 0.5), (515, 2048, 0.2), (37 * world, 515, 0.5)]):
+            M = workloads.bernoulli_matrix(rows, cols, d, seed=30 + i, device=dev, scale=0.02)
+            x = workloads.dense_vector(cols, 70 + i, dev)
+            sh = sharded.shard_rows(M)
+            mats.append((sh, x, sharded.multiply_sharded(sh, x)))
+        pd = sharded.PeerGather(4096, dev, step_rows=3 * 4096 + 64)
+
+        def step():
+            pd.begin_step()
+            ys = [pd.multiply_deferred(sh, x, immutable=True) for sh, x, _ in mats]
+            pd.wait()
+            return ys
+
+        for rep in range(3):
+            ys = step()
+            torch.cuda.synchronize()
+            for (sh, x, ref), y in zip(mats, ys):
+                if not torch.equal(y, ref):
+                    ok, msg = False, f"rank {rank}: deferred step {rep}, {sh.total_rows} rows differ from the all-gather path"
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graphs, outs = [], []
+        for _ in range(2):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                outs.append(step())
+            graphs.append(g)
+        for rep in range(4):
+            for y in outs[rep % 2]:
+                y.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            graphs[rep % 2].replay()
+            torch.cuda.synchronize()
+            for (sh, x, ref), y in zip(mats, outs[rep % 2]):
+                if not torch.equal(y, ref):
+                    ok, msg = False, f"rank {rank}: graph replay {rep}, {sh.total_rows} rows differ"
+        if pd.error_flag() != 0:
+            ok, msg = False, f"rank {rank}: deferred wait gave up on rank {pd.error_flag() - 1}"
+        del graphs, outs
+        pd.close()
+        pg.close()
     except Exception as e:  # noqa: BLE001
         ok, msg = False, f"rank {rank}: {type(e).__name__}: {e}"
     q.put((rank, ok, msg))
     torch.cuda.synchronize()
     dist.barrier()
-    os._exit(0)   # skip NCCL teardown, as bench.py does
+    dist.destroy_process_group()
 
 
 def _decode_worker(rank, world, port, q):
@@ -70,7 +117,7 @@ def _decode_worker(rank, world, port, q):
         from macko_spmv_b200 import llama_decode, sharded
 
         cfg = dict(hidden=256, heads=4, ffn=688, vocab=1000, layers=2, eps=1e-5, rope_theta=10000.0)
-        pg = sharded.PeerGather(max(3 * 256, 2 * 688, 1000), dev)
+        pg = sharded.PeerGather(max(world * 256, 1000), dev)
         with torch.no_grad():
             tp = llama_decode.LlamaDecoder(0.5, cfg=cfg, device=dev, max_len=16, seed=123, peer=pg)
             one = llama_decode.LlamaDecoder(0.5, cfg=cfg, device=dev, max_len=16, seed=123)
@@ -86,12 +133,14 @@ def _decode_worker(rank, world, port, q):
                     ok, msg = False, f"rank {rank}: token {i} rel {rel} same_on_ranks {torch.equal(ref, a)}"
         if pg.error_flag() != 0:
             ok, msg = False, f"rank {rank}: wait gave up on rank {pg.error_flag() - 1}"
+        del tp, one
+        pg.close()
     except Exception as e:  # noqa: BLE001
         ok, msg = False, f"rank {rank}: {type(e).__name__}: {e}"
     q.put((rank, ok, msg))
     torch.cuda.synchronize()
     dist.barrier()
-    os._exit(0)
+    dist.destroy_process_group()
 
 
 def _run(world, target=None):
