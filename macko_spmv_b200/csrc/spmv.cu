@@ -213,9 +213,6 @@ struct Peers {
     int deferred;                 // publish and return: the caller enqueues macko_peer_wait where y is consumed
 };
 
-constexpr unsigned kDebugStageFirst = 0x100u;   // experiment: stage x before the first matrix loads (plain launches)
-constexpr unsigned kDebugPlainCopy = 0x200u;    // experiment: stage x with loads and stores instead of asynchronous copies
-
 // Kernel variants without a scatter epilogue / without a plan take an empty structure in place of the tables:
 // the parameter block of the plain product stays small.
 struct NoPeers {};
@@ -241,7 +238,10 @@ struct Extra {
 // PLAN  rows come from a plan: virtual rows (begin, length, starting column, destination) sorted by length;
 //       the segments of a long row leave fp32 partial sums that the last one to finish adds up in segment order
 // BF    values, x and y are bfloat16 instead of fp16 (same buffers, same decode; fp32 accumulation either way)
-template <int L, int NPAIR, bool XS, bool PEER, int BV = 1, bool PLAN = false, bool BF = false>
+// EARLY the caller has declared the matrix immutable: the first matrix loads are issued before the wait for the
+//       previous kernel of the stream and before x is staged (a separate instantiation, so that the default
+//       launch keeps the simpler code: wait, stage x, then walk the rows)
+template <int L, int NPAIR, bool XS, bool PEER, int BV = 1, bool PLAN = false, bool BF = false, bool EARLY = false>
 __global__ void __launch_bounds__(kThreads, 2)
 spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
             const int *__restrict__ ri, const __half *__restrict__ x, __half *__restrict__ y,
@@ -251,6 +251,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     static_assert(BV == 1 || (XS && !PEER), "batched products gather from shared memory and have no scatter epilogue");
     static_assert(!PLAN || (XS && !PEER && BV == 1), "planned launches are built for the single-vector product with x in shared memory");
     static_assert(!BF || (!PEER && BV == 1 && !PLAN), "bfloat16 is built for the plain single-vector product");
+    static_assert(!EARLY || BV == 1, "early matrix loads are built for the single-vector product");
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int STEP = kGroup * L;   // elements per group per sub-step
     constexpr int D = 2 * NPAIR;       // sub-steps per iteration
@@ -266,8 +267,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     // drain. Memory written by earlier kernels of the stream (x, y, and the matrix unless the caller has
     // declared it immutable) is not touched before griddepcontrol.wait. Both are no-ops for a plain launch.
     asm volatile("griddepcontrol.launch_dependents;");
-    const bool matrix_early = (flags & MACKO_SPMV_MATRIX_IMMUTABLE) != 0u;
-    if (!matrix_early) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- this warp's work: a contiguous row range dealt in blocks of K rows (so that the groups of a warp
     //      run out of rows together), or, planned, every n_warps-th block of K virtual rows of the sorted
@@ -394,9 +394,8 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         __syncthreads();
     }
     };
-    const bool stage_first = (flags & kDebugStageFirst) != 0u && !matrix_early;
-    if (stage_first) stage_x();
-    bool first_pass = true;
+    if constexpr (!EARLY) stage_x();
+    bool first_pass = EARLY;
     for (;;) {
         bool done = false;
         // ---- groups that ran out of work finish their row and take the next one ---------------------
@@ -483,6 +482,10 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
             }
         }
 
+        if constexpr (!EARLY) {
+            if (done) break;
+        }
+
         // ---- issue the loads of the whole iteration ------------------------------------------------------
         uint4 v[D];
         unsigned w[D];
@@ -506,10 +509,12 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
         // ---- first pass only: with the first matrix loads in flight, wait for the previous kernel of the
         //      stream (if that has not happened yet) and stage x into shared memory, framed by zeros. Every
         //      warp comes through here, also one without rows. ---------------------------------------------
-        if (first_pass) {
-            first_pass = false;
-            if (matrix_early) asm volatile("griddepcontrol.wait;" ::: "memory");
-            if (!stage_first) stage_x();
+        if constexpr (EARLY) {
+            if (first_pass) {
+                first_pass = false;
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                stage_x();
+            }
         }
         if (done) break;
 
@@ -734,10 +739,30 @@ bool use_pdl()
     return on;
 }
 
+template <int L, int NPAIR, bool XS, bool PEER, int BV, bool PLAN, bool BF, bool EARLY>
+int launch_variant(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
+                   const void *x, void *y, float alpha, float beta, cudaStream_t stream,
+                   const DeviceInfo &dev, int ctas_per_sm, const Peers &peers, int batch, const Extra &extra);
+
+// The instantiation with or without early matrix loads, by the immutable-matrix flag of the call.
 template <int L, int NPAIR, bool XS, bool PEER = false, int BV = 1, bool PLAN = false, bool BF = false>
 int launch(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
            const void *x, void *y, float alpha, float beta, cudaStream_t stream,
            const DeviceInfo &dev, int ctas_per_sm, const Peers &peers = Peers{}, int batch = 1, const Extra &extra = Extra{})
+{
+    if constexpr (BV == 1) {
+        if (extra.flags & MACKO_SPMV_MATRIX_IMMUTABLE)
+            return launch_variant<L, NPAIR, XS, PEER, BV, PLAN, BF, true>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta,
+                                                                         stream, dev, ctas_per_sm, peers, batch, extra);
+    }
+    return launch_variant<L, NPAIR, XS, PEER, BV, PLAN, BF, false>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta,
+                                                                  stream, dev, ctas_per_sm, peers, batch, extra);
+}
+
+template <int L, int NPAIR, bool XS, bool PEER, int BV, bool PLAN, bool BF, bool EARLY>
+int launch_variant(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
+                   const void *x, void *y, float alpha, float beta, cudaStream_t stream,
+                   const DeviceInfo &dev, int ctas_per_sm, const Peers &peers, int batch, const Extra &extra)
 {
     size_t smem = XS ? (size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) * BV : 0;
     if (PEER)  // staging area for a CTA's slice of y (a CTA never owns more rows than rows / #SMs + rounding)
@@ -745,7 +770,7 @@ int launch(const void *values, const void *deltas, const int32_t *ri, int rows, 
     if (smem > (size_t)dev.max_smem_optin)
         return fail(MACKO_ERR_INVALID_ARGUMENT, "the launch needs %lld bytes of shared memory, the device offers %d (cols=%d)",
                     (long long)smem, dev.max_smem_optin, cols);
-    auto kernel = spmv_kernel<L, NPAIR, XS, PEER, BV, PLAN, BF>;
+    auto kernel = spmv_kernel<L, NPAIR, XS, PEER, BV, PLAN, BF, EARLY>;
     if (smem > 48 * 1024) {
         // Idempotent and cheap; set on every call so that every device is covered.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -886,15 +911,6 @@ int check_args(const void *values, const void *deltas, const int32_t *ri, int64_
 namespace macko {
 namespace {
 
-unsigned debug_flags()
-{
-    static const unsigned bits = [] {
-        const char *v = getenv("MACKO_SPMV_DEBUG");
-        return v ? (unsigned)strtoul(v, nullptr, 0) & 0x300u : 0u;
-    }();
-    return bits;
-}
-
 int check_flags(uint32_t flags)
 {
     if (flags & ~(uint32_t)MACKO_SPMV_MATRIX_IMMUTABLE)
@@ -923,7 +939,7 @@ int spmv_default(const void *values, const void *deltas, const int32_t *row_indi
     const bool xs = smem <= (size_t)dev->max_smem_optin;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     Extra extra = {};
-    extra.flags = flags | debug_flags();
+    extra.flags = flags;
     if (xs)
         return launch_l<true, BF>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
     return launch_l<false, BF>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
