@@ -683,8 +683,9 @@ def run_own_arm(args):
     rows8 = lambda r: (r + 7) // 8 * 8
     step_rows = max(sum(rows8(c["rows"]) for c in cases), sum(rows8(r) for r, _ in workloads.SHARDED_SHAPES) * 2)
     peer = None
-    if world > 1 and args.exchange == "peer":
-        peer = sharded.PeerGather(max(c["rows"] for c in cases), device, step_rows=step_rows)
+    if world > 1 and args.exchange in ("peer", "peer-fused"):
+        peer = sharded.PeerGather(max(c["rows"] for c in cases), device, step_rows=step_rows,
+                                  overlap_forward=(args.exchange == "peer"))
     ys_local = [torch.empty(c["hi"] - c["lo"], dtype=torch.float16, device=device) for c in cases]
     ys_full = [torch.empty(c["rows"], dtype=torch.float16, device=device) for c in cases] if world > 1 else ys_local
     flag = cabi.SPMV_MATRIX_IMMUTABLE   # the matrices are weights: compressed at set-up, never written again
@@ -908,7 +909,7 @@ def run_own_arm(args):
     line = None
     if rank == 0:
         achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
-        launches_per_step = n_cases + (1 if peer is not None else 0)
+        launches_per_step = n_cases + (0 if peer is None else (n_cases + 1 if peer.overlap_forward else 1))
         large_fracs = [c["per_gpu_roofline_frac"] for c in large["cases"]] if large else []
         if per_case:
             large_fracs += [p["roofline_frac"] for p in per_case if p["shape"][0] * p["shape"][1] >= 8192 * 8192]
@@ -918,7 +919,7 @@ def run_own_arm(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
             "config": {
                 "workload": WORKLOAD,
-                "parallelism": "single GPU" if world == 1 else (f"rows of every matrix split over {world} GPUs; " + ("every SpMV kernel stores its y slice into all ranks' y over NVLink and publishes its arrival; one bounded wait per step for all 36 (no collective)" if peer is not None else "NCCL all-gather of y after each SpMV")),
+                "parallelism": "single GPU" if world == 1 else (f"rows of every matrix split over {world} GPUs; " + (("every SpMV writes its rows into this rank's y; a forward kernel on a graph branch copies them into all ranks' y over NVLink and publishes the arrival beside the next products; one bounded wait per step for all 36 (no collective)" if peer.overlap_forward else "every SpMV kernel stores its y slice into all ranks' y over NVLink and publishes its arrival; one bounded wait per step for all 36 (no collective)") if peer is not None else "NCCL all-gather of y after each SpMV")),
                 "l2": "inputs larger than L2: a step streams %.2f GB of distinct compressed data per GPU, each matrix once" % (step_bytes / 1e9),
                 "launch": ("one CUDA graph per step" if used_graph else "eager launches")
                           + "; matrices declared immutable (weights compressed at set-up): first matrix loads may precede the end of the previous kernel",
@@ -1073,8 +1074,9 @@ def main():
     ap.add_argument("--decode-layers", type=int, default=32)
     ap.add_argument("--decode-prompt", type=int, default=16)
     ap.add_argument("--decode-tokens", type=int, default=48)
-    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
-                    help="N > 1: how the y slices are exchanged (fused peer stores, or NCCL all-gather)")
+    ap.add_argument("--exchange", choices=["peer", "peer-fused", "nccl"], default="peer",
+                    help="N > 1: how the y slices are exchanged: peer stores by a forward kernel beside the next products, "
+                         "peer stores from the tail of the product kernel, or NCCL all-gather")
     ap.add_argument("--single", default=None, metavar="ROWS,COLS,DENSITY",
                     help="run only a few products on one matrix (small case for profiler captures)")
     ap.add_argument("--single-kind", default="plain",

@@ -317,6 +317,21 @@ int macko_spmv_fp16_scatter_ex(const void *values, const void *deltas, const int
                                int rank, int world, uint32_t flags, uint32_t spin_limit, void *stream);
 int macko_peer_wait_limited(uint32_t *local_flags, int world, uint32_t spin_limit, void *stream);
 
+/*
+ * The exchange step alone, for hosts that overlap it with further products: rank `rank` has written rows
+ * [row_offset, row_offset + rows) of y into its own full-y buffer `peer_y[rank]` with an ordinary product
+ * (macko_spmv_fp16_ex with y = peer_y[rank] + row_offset); this call enqueues one small kernel that copies
+ * those rows into `peer_y[p]` of every other rank, makes them visible system-wide and publishes the rank's
+ * arrival counter in every rank's flag array, exactly like the tail of macko_spmv_fp16_scatter_ex with
+ * MACKO_SCATTER_DEFERRED_WAIT. Enqueue it behind the product (same stream, or another stream / graph branch
+ * that waits for the product), and macko_peer_wait behind all forwards before the full y is read. The
+ * product kernel then has no epilogue at all and the NVLink round trip of the exchange runs beside the next
+ * products. Same tables, same counters and same buffer-reuse rule as the scatter calls; calls of one rank must
+ * not overlap each other (they share the rank's call counter). No counterpart in the reference.
+ */
+int macko_peer_forward(void *const *peer_y, int64_t row_offset, int64_t rows, uint32_t *const *peer_flags,
+                       int rank, int world, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -66,6 +66,7 @@ SIGNATURES = {
     "macko_peer_wait": (_int, [_vp, _int, _vp]),
     "macko_spmv_fp16_scatter_ex": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _int, _int, _u32, _u32, _vp]),
     "macko_peer_wait_limited": (_int, [_vp, _int, _u32, _vp]),
+    "macko_peer_forward": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp]),
 }
 
 

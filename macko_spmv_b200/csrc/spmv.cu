@@ -712,6 +712,39 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     }
 }
 
+// One CTA: copies rows [row_offset, row_offset + rows) of this rank's full y into the full y of every other rank,
+// makes them visible system-wide and publishes this rank's arrival counter everywhere: the exchange step of a
+// row-sharded product as a kernel of its own, for callers that run it beside the next products (on another
+// stream or graph branch) instead of at the tail of the product kernel.
+__global__ void __launch_bounds__(kThreads) peer_forward_kernel(const Peers peers, int rows)
+{
+    const int tid = threadIdx.x;
+    const unsigned short *src = reinterpret_cast<const unsigned short *>(peers.y[peers.rank] + peers.row_offset);
+    bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+    for (int p = 0; p < peers.world; ++p)
+        vec = vec && ((reinterpret_cast<uintptr_t>(peers.y[p] + peers.row_offset) & 15) == 0);
+    const int chunks = vec ? rows >> 3 : 0;
+    for (int c = tid; c < chunks; c += kThreads) {
+        const uint4 val = __ldcg(reinterpret_cast<const uint4 *>(src) + c);
+        for (int p = 0; p < peers.world; ++p)
+            if (p != peers.rank) reinterpret_cast<uint4 *>(peers.y[p] + peers.row_offset)[c] = val;
+    }
+    for (int i = (chunks << 3) + tid; i < rows; i += kThreads) {
+        const unsigned short val = __ldcg(src + i);
+        for (int p = 0; p < peers.world; ++p)
+            if (p != peers.rank) reinterpret_cast<unsigned short *>(peers.y[p] + peers.row_offset)[i] = val;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence_system();   // cumulative over what the barrier ordered before it: the forwarded slice is out
+        unsigned *mine = peers.flags[peers.rank];
+        const unsigned seq = mine[peers.world] + 1u;
+        mine[peers.world] = seq;
+        for (int p = 0; p < peers.world; ++p)
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + peers.rank), "r"(seq) : "memory");
+    }
+}
+
 // Waits (bounded) until every rank's arrival counter has reached this rank's own call counter, i.e.
 // until all slices of the row-sharded products issued so far have landed in this rank's full y.
 __global__ void peer_wait_kernel(unsigned *flags, int world, unsigned spin_limit)
@@ -1176,6 +1209,31 @@ int macko_spmv_fp16_scatter(const void *values, const void *deltas, const int32_
 {
     return macko_spmv_fp16_scatter_ex(values, deltas, row_indices, rows, cols, padded_count, x, peer_y, row_offset,
                                       peer_flags, rank, world, 0u, 0u, stream);
+}
+
+int macko_peer_forward(void *const *peer_y, int64_t row_offset, int64_t rows, uint32_t *const *peer_flags,
+                       int rank, int world, void *stream)
+{
+    using namespace macko;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "rank %d / world %d outside 1..%d", rank, world, kMaxPeers);
+    if (!peer_y || !peer_flags || row_offset < 0 || rows < 0 || rows >= (1LL << 31))
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "null peer tables, negative row offset or bad row count");
+    Peers peers = {};
+    for (int p = 0; p < world; ++p) {
+        if (!peer_y[p] || !peer_flags[p]) return fail(MACKO_ERR_INVALID_ARGUMENT, "null pointer for rank %d", p);
+        if (!aligned(peer_y[p], 2) || !aligned(peer_flags[p], 4))
+            return fail(MACKO_ERR_MISALIGNED, "peer buffers need 2-byte (y) and 4-byte (flags) alignment");
+        peers.y[p] = static_cast<__half *>(peer_y[p]);
+        peers.flags[p] = peer_flags[p];
+    }
+    peers.row_offset = row_offset;
+    peers.world = world;
+    peers.rank = rank;
+    peer_forward_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(peers, (int)rows);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "peer forward launch: %s", cudaGetErrorString(e));
+    return MACKO_OK;
 }
 
 int macko_peer_wait_limited(uint32_t *local_flags, int world, uint32_t spin_limit, void *stream)

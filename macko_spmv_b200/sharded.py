@@ -132,15 +132,17 @@ class PeerGather:
       consecutive calls must never use the same slot (a faster rank writes its slice of the next product while
       a slower one may still read the previous y): a fixed sequence with an odd number of calls that is
       replayed again and again (a captured decode step) gives one of its calls `slot=2`, the spare slot.
-    * `begin_step()`, then any number of `multiply_deferred(shard, x)`, then `wait()`: every product
-      publishes its slice and returns at once (it overlaps with the next product like an ordinary kernel);
-      each gets its own region of the step's half of the buffer, and one bounded wait kernel at the end
-      makes all of them complete. The two halves alternate from step to step: a rank that is already in
+    * `begin_step()`, then any number of `multiply_deferred(shard, x)`, then `wait()`: every product writes
+      its rows into this rank's own buffer with the ordinary kernel; a small forward kernel on a side stream
+      (a branch of the graph when captured) copies them to the other ranks and publishes the arrival, beside
+      the next products (`overlap_forward=False`: the scatter kernel does both, without waiting). Each product
+      gets its own region of the step's half of the buffer, and one bounded wait kernel at the end makes all
+      of them complete. The two halves alternate from step to step: a rank that is already in
       step s + 1 writes into the half nobody reads any more, because it passed `wait()` of step s only
       after every rank had delivered step s, i.e. had already consumed step s - 1 in stream order.
     """
 
-    def __init__(self, max_rows: int, device, group=None, step_rows: int = 0):
+    def __init__(self, max_rows: int, device, group=None, step_rows: int = 0, overlap_forward: bool = True):
         import ctypes
         import os
 
@@ -178,6 +180,9 @@ class PeerGather:
         self._half = 1
         self._cursor = 0
         self.spin_limit = 0   # 0 = library default (2^23 polls)
+        self.overlap_forward = bool(overlap_forward)
+        self._side = torch.cuda.Stream(device=device)
+        self._side_busy = False
 
     def _table(self, half: int, offset: int):
         key = (half, offset)
@@ -221,14 +226,32 @@ class PeerGather:
             raise ValueError(f"the step's products need more than the {self.step_rows} rows the buffers hold")
         off = self._cursor
         self._cursor += rows8
-        flags = self._cabi.SCATTER_DEFERRED_WAIT | (self._cabi.SPMV_MATRIX_IMMUTABLE if immutable else 0)
-        self._launch(shard, x, self._table(self._half, off), flags)
+        table = self._table(self._half, off)
+        if not self.overlap_forward:
+            flags = self._cabi.SCATTER_DEFERRED_WAIT | (self._cabi.SPMV_MATRIX_IMMUTABLE if immutable else 0)
+            self._launch(shard, x, table, flags)
+            return self.buf[self._half, off : off + shard.total_rows]
+        comp = shard.compressed
+        main = torch.cuda.current_stream()
+        y_own = int(table[self.rank]) + 2 * shard.row_lo
+        self.check(self.lib, self.lib.macko_spmv_fp16_ex(
+            comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
+            x.data_ptr(), y_own, 1.0, 0.0, self._cabi.SPMV_MATRIX_IMMUTABLE if immutable else 0, main.cuda_stream))
+        done = torch.cuda.Event()
+        done.record(main)
+        self._side.wait_event(done)
+        self.check(self.lib, self.lib.macko_peer_forward(table, shard.row_lo, comp[3], self._flag_table, self.rank,
+                                                         self.world, self._side.cuda_stream))
+        self._side_busy = True
         return self.buf[self._half, off : off + shard.total_rows]
 
     def wait(self) -> None:
         """Enqueue the bounded wait for the slices of all ranks of every product issued so far."""
-        stream = torch.cuda.current_stream().cuda_stream
-        self.check(self.lib, self.lib.macko_peer_wait_limited(self._local_flags, self.world, self.spin_limit, stream))
+        main = torch.cuda.current_stream()
+        if self._side_busy:
+            main.wait_stream(self._side)   # the forwards of this step (joins the side branch when captured)
+            self._side_busy = False
+        self.check(self.lib, self.lib.macko_peer_wait_limited(self._local_flags, self.world, self.spin_limit, main.cuda_stream))
 
     def error_flag(self) -> int:
         """0, or 1 + the rank whose slice never arrived in some earlier wait (reads device memory)."""

@@ -341,11 +341,13 @@ def test_bounded_wait_runs_out_and_says_who_was_missing():
     assert torch.equal(macko_spmv.multiply(comp, x), ref)
 
 
+@pytest.mark.parametrize("split", [False, True])
 @pytest.mark.parametrize("world", [2, 3, 8])
-def test_deferred_exchange_all_ranks_on_one_gpu(world):
+def test_deferred_exchange_all_ranks_on_one_gpu(world, split):
     """The N-rank data path of the fused exchange with every rank's buffers in this GPU's memory: each rank's
     product forwards its slice to all "peers" and publishes its counter without waiting (deferred), then
-    every rank's wait kernel runs. No kernel waits for a later one, so one stream on one GPU is enough."""
+    every rank's wait kernel runs. No kernel waits for a later one, so one stream on one GPU is enough.
+    `split`: the exchange as a kernel of its own (macko_peer_forward) behind an ordinary product."""
     lib = cabi.load()
     stream = _stream()
     ptrs = ctypes.c_void_p * world
@@ -362,6 +364,12 @@ def test_deferred_exchange_all_ranks_on_one_gpu(world):
                 lo, hi = sharded.row_block(rows, r, world)
                 comp = macko_spmv.compress(M[lo:hi].contiguous())
                 full[lo:hi] = macko_spmv.multiply(comp, x)
+                if split:   # the product into the rank's own buffer, then the forward kernel
+                    cabi.check(lib, lib.macko_spmv_fp16_ex(
+                        comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
+                        x.data_ptr(), ys[r].data_ptr() + 2 * lo, 1.0, 0.0, cabi.SPMV_MATRIX_IMMUTABLE * (rep == 1), stream))
+                    cabi.check(lib, lib.macko_peer_forward(ytab, lo, hi - lo, ftab, r, world, stream))
+                    continue
                 cabi.check(lib, lib.macko_spmv_fp16_scatter_ex(
                     comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
                     x.data_ptr(), ytab, lo, ftab, r, world,

@@ -56,42 +56,41 @@ def _worker(rank, world, port, q):
             x = workloads.dense_vector(cols, 70 + i, dev)
             sh = sharded.shard_rows(M)
             mats.append((sh, x, sharded.multiply_sharded(sh, x)))
-        pd = sharded.PeerGather(4096, dev, step_rows=3 * 4096 + 64)
+        for overlap in (True, False):   # exchange by a forward kernel on a side stream / at the tail of the product kernel
+            pd = sharded.PeerGather(4096, dev, step_rows=3 * 4096 + 64, overlap_forward=overlap)
 
-        def step():
-            pd.begin_step()
-            ys = [pd.multiply_deferred(sh, x, immutable=True) for sh, x, _ in mats]
-            pd.wait()
-            return ys
+            def step():
+                pd.begin_step()
+                ys = [pd.multiply_deferred(sh, x, immutable=True) for sh, x, _ in mats]
+                pd.wait()
+                return ys
 
-        for rep in range(3):
-            ys = step()
-            torch.cuda.synchronize()
-            for (sh, x, ref), y in zip(mats, ys):
-                if not torch.equal(y, ref):
-                    ok, msg = False, f"rank {rank}: deferred step {rep}, {sh.total_rows} rows differ from the all-gather path"
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        graphs, outs = [], []
-        for _ in range(2):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                outs.append(step())
-            graphs.append(g)
-        for rep in range(4):
-            for y in outs[rep % 2]:
-                y.zero_()
-            torch.cuda.synchronize()
-            dist.barrier()
-            graphs[rep % 2].replay()
-            torch.cuda.synchronize()
-            for (sh, x, ref), y in zip(mats, outs[rep % 2]):
-                if not torch.equal(y, ref):
-                    ok, msg = False, f"rank {rank}: graph replay {rep}, {sh.total_rows} rows differ"
-        if pd.error_flag() != 0:
-            ok, msg = False, f"rank {rank}: deferred wait gave up on rank {pd.error_flag() - 1}"
-        del graphs, outs
-        pd.close()
+            for rep in range(3):
+                ys = step()
+                torch.cuda.synchronize()
+                for (sh, x, ref), y in zip(mats, ys):
+                    if not torch.equal(y, ref):
+                        ok, msg = False, f"rank {rank}: deferred step {rep}, {sh.total_rows} rows differ from the all-gather path"
+            graphs, outs = [], []
+            for _ in range(2):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    outs.append(step())
+                graphs.append(g)
+            for rep in range(4):
+                for y in outs[rep % 2]:
+                    y.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
+                graphs[rep % 2].replay()
+                torch.cuda.synchronize()
+                for (sh, x, ref), y in zip(mats, outs[rep % 2]):
+                    if not torch.equal(y, ref):
+                        ok, msg = False, f"rank {rank}: graph replay {rep}, {sh.total_rows} rows differ"
+            if pd.error_flag() != 0:
+                ok, msg = False, f"rank {rank}: deferred wait gave up on rank {pd.error_flag() - 1}"
+            del graphs, outs
+            pd.close()
         pg.close()
     except Exception as e:  # noqa: BLE001
         ok, msg = False, f"rank {rank}: {type(e).__name__}: {e}"
