@@ -999,7 +999,8 @@ def run_own_arm(args):
 
 def run_single_case(args):
     """A few SpMVs on one synthetic matrix: the small workload profiler captures are taken on.
-    `--single-kind`: plain (default launch), planned, batched8, scatter (world of one), decompress, compress."""
+    `--single-kind`: plain (default launch), frozen (immutable matrix: early loads), planned, batched8, scatter (world of
+    one), decompress, compress."""
     import ctypes
 
     import macko_spmv_b200 as macko_spmv
@@ -1019,6 +1020,9 @@ def run_single_case(args):
     kind = args.single_kind
     if kind == "plain":
         run = lambda: macko_spmv.multiply(comp, x)
+    elif kind == "frozen":
+        fz0 = macko_spmv.freeze(comp, plan=False)
+        run = lambda: macko_spmv.multiply(fz0, x)
     elif kind == "planned":
         fz = macko_spmv.freeze(comp, plan=True)
         run = lambda: macko_spmv.multiply(fz, x)
@@ -1053,7 +1057,7 @@ def run_single_case(args):
     nbytes = workloads.algorithmic_bytes(comp[0].numel(), rows, cols)
     res = {"single": [rows, cols, density], "kind": kind, "us_warm_l2": e0.elapsed_time(e1) * 1000 / args.steps,
            "algorithmic_bytes": nbytes}
-    if kind in ("plain", "planned", "batched8", "scatter"):
+    if kind in ("plain", "frozen", "planned", "batched8", "scatter"):
         ref = M.float() @ x.float()
         res["rel_l2_vs_dense_fp32"] = float((y.float() - ref).norm() / ref.norm())
     print(json.dumps(res), flush=True)
@@ -1080,7 +1084,7 @@ def main():
     ap.add_argument("--single", default=None, metavar="ROWS,COLS,DENSITY",
                     help="run only a few products on one matrix (small case for profiler captures)")
     ap.add_argument("--single-kind", default="plain",
-                    choices=["plain", "planned", "batched8", "scatter", "decompress", "compress"])
+                    choices=["plain", "frozen", "planned", "batched8", "scatter", "decompress", "compress"])
     args = ap.parse_args()
     if args.single:
         run_single_case(args)

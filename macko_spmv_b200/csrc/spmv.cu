@@ -355,14 +355,12 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     if (BV > 1) {
         __half *xs = reinterpret_cast<__half *>(smem);
         const int n_total = (kXPadFront + cols + kXPadBack) * BV;
-#pragma unroll 1
         for (int i = tid; i < kXPadFront * BV; i += kThreads) xs[i] = __ushort_as_half(0);
-#pragma unroll 1
         for (int i = (kXPadFront + cols) * BV + tid; i < n_total; i += kThreads) xs[i] = __ushort_as_half(0);
 #pragma unroll
         for (int b = 0; b < BV; ++b) {
             const __half *xb = x + (size_t)b * cols;
-#pragma unroll 1
+#pragma unroll 4
             for (int c = tid; c < cols; c += kThreads)
                 xs[(size_t)(kXPadFront + c) * BV + b] = b < batch ? xb[c] : __ushort_as_half(0);
         }

@@ -170,7 +170,8 @@ class ColumnShardedMackoLinear(nn.Module):
             raise RuntimeError(f"expected this rank's {self.in_local} input features, got {tuple(x_local.shape)}")
         final = self.c_0.data_ptr() == self._c0_ptr
         parts = self.peer.multiply(self.shard, x_local.contiguous(), immutable=final)
-        return parts.view(self.peer.world, self.out_features).sum(dim=0, dtype=torch.float32).to(torch.float16)
+        # one reduction kernel: torch adds fp16 inputs in fp32 and rounds once, in rank order on every rank
+        return parts.view(self.peer.world, self.out_features).sum(dim=0)
 
 
 def compress_state_dict(state_dict, select=lambda name: ("self_attn" in name or "mlp" in name) and name.endswith(".weight")):
