@@ -99,6 +99,17 @@ int macko_spmv_bf16(const void *values, const void *deltas, const int32_t *row_i
                     const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream);
 
 /*
+ * The same product for int8 values: values int8[P] (8-byte aligned), x and y fp16, fp32 accumulation; the
+ * bytes are converted exactly to fp16 in registers and go through the same fused multiply-add.
+ * Replaces: kernel `macko_spmv_int8<reuse_value_from_c>` (src/macko_spmv/cuda/kernels.cuh:127-216), which the
+ * reference launches from its C benchmark only (c_benchmarking/benchmark.cu:106-119, kernel id 8).
+ * Matrices come from macko_compress_count_int8 / macko_compress_emit_int8.
+ */
+int macko_spmv_int8(const void *values, const void *deltas, const int32_t *row_indices,
+                    int64_t rows, int64_t cols, int64_t padded_count,
+                    const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream);
+
+/*
  * Same product with the kernel shape chosen by the caller, for tuning sweeps:
  *   lanes_per_row in {4, 8, 16, 32}; steps_in_flight in {2, 4, 6};
  *   x_in_shared 0/1; ctas_per_sm >= 1 (0 = library default).
@@ -229,6 +240,19 @@ int macko_compress_emit(const void *dense, int64_t rows, int64_t cols,
  * reference has no bf16 path (README.md:167 lists more value types as wanted); the layout is its fp16 layout.
  */
 int macko_compress_emit_bf16(const void *dense, int64_t rows, int64_t cols,
+                             const int32_t *row_indices, int64_t padded_count,
+                             void *values, void *deltas,
+                             void *workspace, int64_t workspace_bytes, void *stream);
+
+/*
+ * The compressor for int8 matrices, both phases (dense: int8[rows*cols]; values: int8[P]; same deltas and
+ * row_indices as above). Bit-identical to the reference's int8 encoder `compress_rows_int8_cpu`
+ * (src/macko_spmv/cuda/cpu_compressor.cuh:75-117), which, unlike its fp16 encoder, keeps the pads inside the
+ * zeros at the end of a row: a row that ends in t zeros (an empty row: t = cols) stores floor(t / 16) pads there.
+ */
+int macko_compress_count_int8(const void *dense, int64_t rows, int64_t cols,
+                              int32_t *row_indices, void *stream);
+int macko_compress_emit_int8(const void *dense, int64_t rows, int64_t cols,
                              const int32_t *row_indices, int64_t padded_count,
                              void *values, void *deltas,
                              void *workspace, int64_t workspace_bytes, void *stream);

@@ -62,8 +62,8 @@ def native_version() -> int:
 
 @torch.library.register_fake("macko_spmv::multiply")
 def _multiply_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, V):
-    # Same meta kernel as the reference (src/macko_spmv/__init__.py:105-107).
-    return torch.empty((M_rows,), device=M_values.device, dtype=M_values.dtype)
+    # Same meta kernel as the reference (src/macko_spmv/__init__.py:105-107); int8 values give fp16 like V.
+    return torch.empty((M_rows,), device=M_values.device, dtype=V.dtype)
 
 
 @torch.library.register_fake("macko_spmv::compress_dense")
@@ -88,7 +88,7 @@ def _decompress_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols):
 
 @torch.library.register_fake("macko_spmv::multiply_frozen")
 def _multiply_frozen_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, V):
-    return torch.empty((M_rows,), device=M_values.device, dtype=M_values.dtype)
+    return torch.empty((M_rows,), device=M_values.device, dtype=V.dtype)
 
 
 @torch.library.register_fake("macko_spmv::multiply_planned")

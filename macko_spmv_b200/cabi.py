@@ -48,6 +48,7 @@ SIGNATURES = {
     "macko_spmv_fp16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _vp]),
     "macko_spmv_fp16_ex": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _u32, _vp]),
     "macko_spmv_bf16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _u32, _vp]),
+    "macko_spmv_int8": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f, _f, _u32, _vp]),
     "macko_spmv_plan_bytes": (_i64, [_i64, _i64, _i64, _i32]),
     "macko_spmv_plan": (_int, [_vp, _vp, _i64, _i64, _i64, _i32, _vp, _i64, ctypes.POINTER(PlanInfo), _vp]),
     "macko_spmv_fp16_planned": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, ctypes.POINTER(PlanInfo), _vp, _vp, _f, _f, _u32, _vp]),
@@ -59,6 +60,8 @@ SIGNATURES = {
     "macko_compress_workspace_bytes": (_i64, [_i64]),
     "macko_compress_emit": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
     "macko_compress_emit_bf16": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "macko_compress_count_int8": (_int, [_vp, _i64, _i64, _vp, _vp]),
+    "macko_compress_emit_int8": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
     "macko_compress_emit_static": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "macko_compress_static_capacity": (_i64, []),
     "macko_compress_overflow": (_int, [ctypes.POINTER(_u32), _vp]),

@@ -258,9 +258,10 @@ __global__ void __launch_bounds__(1024) scan_rows_kernel(int *__restrict__ ri, i
 
 // Packs 8 one-per-byte deltas into 4 bytes, zeroing everything at or beyond n = ri[rows];
 // also zeroes values[n..P).
+template <typename V>
 __global__ void __launch_bounds__(256)
 pack_kernel(const uint2 *__restrict__ nibbles8, const int *__restrict__ ri, int rows, int groups,
-            unsigned *__restrict__ deltas32, unsigned short *__restrict__ values)
+            unsigned *__restrict__ deltas32, V *__restrict__ values)
 {
     const int g = blockIdx.x * 256 + threadIdx.x;
     if (g >= groups) return;   // every read and write below stays under 8 * groups = P
@@ -285,14 +286,119 @@ pack_kernel(const uint2 *__restrict__ nibbles8, const int *__restrict__ ri, int 
     }
 }
 
-int check_dense(const void *dense, int64_t rows, int64_t cols)
+// ---- int8 values ---------------------------------------------------------------------------------------
+// The reference's int8 encoder (src/macko_spmv/cuda/cpu_compressor.cuh:75-117) differs from the fp16 one in
+// two ways: a value is one signed byte, and trailing pads stay: a run of t zeros at the end of a row (or a
+// whole empty row, t = cols) still emits floor(t / 16) pads (value 0, delta 15). Same walk as above, one warp
+// per row, 8 columns per lane and step (one 64-bit load when the matrix is 8-byte aligned).
+__device__ __forceinline__ void load8_bytes(const signed char *dense, long long g0, long long total, bool vec_ok,
+                                            unsigned (&w)[2])
+{
+    if (vec_ok && g0 >= 0 && g0 + 8 <= total) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(dense + g0));
+        w[0] = v.x; w[1] = v.y;
+    } else {
+        w[0] = w[1] = 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const long long g = g0 + j;
+            const unsigned b = (g >= 0 && g < total) ? (unsigned)(unsigned char)__ldg(dense + g) : 0u;
+            w[j >> 2] |= b << (8 * (j & 3));
+        }
+    }
+}
+
+__device__ __forceinline__ unsigned nonzero_bytes(const unsigned (&w)[2])
+{
+    unsigned nz = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) nz |= (((w[j >> 2] >> (8 * (j & 3))) & 0xffu) != 0u ? 1u : 0u) << j;
+    return nz;
+}
+
+template <bool EMIT>
+__global__ void __launch_bounds__(kThreads)
+compress_rows_int8_kernel(const signed char *__restrict__ dense, int rows, int cols, bool vec_ok,
+                          int *__restrict__ row_counts_out, const int *__restrict__ row_indices,
+                          signed char *__restrict__ values, unsigned char *__restrict__ nibbles, int limit)
+{
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const long long total = (long long)rows * cols;
+    const long long row_lo = (long long)row * cols;
+    const long long row_hi = row_lo + cols;
+    const long long first = vec_ok ? (row_lo & ~7LL) : row_lo;
+    int carry_prev = -1;
+    int count = 0;
+    int out = EMIT ? row_indices[row] : 0;
+    bool refused = false;
+    for (long long group0 = first; group0 < row_hi; group0 += kColsPerStep) {
+        const long long g0 = group0 + (long long)lane * kColsPerLane;
+        unsigned w[2];
+        load8_bytes(dense, g0, total, vec_ok, w);
+        const int c0 = (int)(g0 - row_lo);
+        const unsigned nz = nonzero_bytes(w) & row_bits(g0, row_lo, row_hi);
+        const unsigned any = __ballot_sync(0xffffffffu, nz != 0);
+        if (any == 0) continue;
+        const int my_last = c0 + (31 - __clz(nz | 1u));
+        int prev = prev_nonzero_before_lane(any, lane, my_last, carry_prev);
+        carry_prev = __shfl_sync(0xffffffffu, my_last, 31 - __clz(any));
+        int mine = __popc(nz);
+        if (nz) mine += (c0 + (__ffs(nz) - 1) - prev - 1) >> 4;
+        if (!EMIT) {
+            count += mine;
+        } else {
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            int k = out + incl - mine;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (nz & (1u << i)) {
+                    const int c = c0 + i;
+                    for (int p = prev + 16; p < c; p += 16) {
+                        if ((unsigned)k < (unsigned)limit) { values[k] = 0; nibbles[k] = 15; } else refused = true;
+                        ++k;
+                    }
+                    if ((unsigned)k < (unsigned)limit) {
+                        values[k] = (signed char)((w[i >> 2] >> (8 * (i & 3))) & 0xffu);
+                        nibbles[k] = (unsigned char)((c - prev - 1) & 15);
+                    } else {
+                        refused = true;
+                    }
+                    ++k;
+                    prev = c;
+                }
+            }
+            out += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    }
+    // pads inside the zeros behind the last non-zero (the whole row when it has none)
+    const int trailing = (cols - 1 - carry_prev) >> 4;
+    if (!EMIT) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
+        if (lane == 0) row_counts_out[row + 1] = count + trailing;
+    } else {
+        for (int i = lane; i < trailing; i += 32) {
+            if ((unsigned)(out + i) < (unsigned)limit) { values[out + i] = 0; nibbles[out + i] = 15; } else refused = true;
+        }
+        if (__any_sync(0xffffffffu, refused) && lane == 0) atomicAdd(&g_compress_overflow, 1u);
+    }
+}
+
+int check_dense(const void *dense, int64_t rows, int64_t cols, uintptr_t element_bytes = 2)
 {
     if (rows < 0 || cols < 0) return fail(MACKO_ERR_INVALID_ARGUMENT, "negative size (rows=%lld cols=%lld)", (long long)rows, (long long)cols);
     if (rows > 0 && cols > 0 && rows > ((1LL << 31) - 1) / cols)
         return fail(MACKO_ERR_SIZE_OVERFLOW, "rows*cols = %lld*%lld does not fit 31 bits", (long long)rows, (long long)cols);
     if (rows >= (1LL << 31) - 1) return fail(MACKO_ERR_SIZE_OVERFLOW, "too many rows");
     if (rows * cols > 0 && !dense) return fail(MACKO_ERR_INVALID_ARGUMENT, "null dense matrix");
-    if (!aligned(dense, 2)) return fail(MACKO_ERR_MISALIGNED, "dense must be 2-byte aligned");
+    if (!aligned(dense, element_bytes)) return fail(MACKO_ERR_MISALIGNED, "dense must be aligned to its element size");
     return MACKO_OK;
 }
 
@@ -394,7 +500,7 @@ static int compress_emit_typed(const void *dense, int64_t rows, int64_t cols, co
         if (st != MACKO_OK) return st;
     }
     const int groups = (int)(padded_count / 8);
-    pack_kernel<<<(groups + 255) / 256, 256, 0, s>>>(
+    pack_kernel<unsigned short><<<(groups + 255) / 256, 256, 0, s>>>(
         static_cast<const uint2 *>(workspace), row_indices, (int)rows, groups,
         static_cast<unsigned *>(deltas), static_cast<unsigned short *>(values));
     return launch_error("pack launch");
@@ -414,6 +520,58 @@ int macko_compress_emit_bf16(const void *dense, int64_t rows, int64_t cols, cons
 {
     return compress_emit_typed(dense, rows, cols, row_indices, padded_count, values, deltas, workspace, workspace_bytes,
                                stream, 0x7f80u);
+}
+
+int macko_compress_count_int8(const void *dense, int64_t rows, int64_t cols, int32_t *row_indices, void *stream)
+{
+    using namespace macko;
+    int st = check_dense(dense, rows, cols, 1);
+    if (st != MACKO_OK) return st;
+    if (!row_indices) return fail(MACKO_ERR_INVALID_ARGUMENT, "null row_indices");
+    if (!aligned(row_indices, 4)) return fail(MACKO_ERR_MISALIGNED, "row_indices must be 4-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (rows > 0) {
+        const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+        compress_rows_int8_kernel<false><<<grid, kThreads, 0, s>>>(
+            static_cast<const signed char *>(dense), (int)rows, (int)cols, aligned(dense, 8), row_indices, nullptr, nullptr,
+            nullptr, 0);
+        st = launch_error("int8 compress count launch");
+        if (st != MACKO_OK) return st;
+    }
+    return launch_row_scan(row_indices, (int)rows, s);
+}
+
+int macko_compress_emit_int8(const void *dense, int64_t rows, int64_t cols, const int32_t *row_indices,
+                             int64_t padded_count, void *values, void *deltas,
+                             void *workspace, int64_t workspace_bytes, void *stream)
+{
+    using namespace macko;
+    int st = check_dense(dense, rows, cols, 1);
+    if (st != MACKO_OK) return st;
+    if (!row_indices) return fail(MACKO_ERR_INVALID_ARGUMENT, "null row_indices");
+    if (padded_count < 0 || padded_count % 8 != 0 || padded_count >= (1LL << 31))
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "padded_count %lld must be a non-negative multiple of 8 below 2^31", (long long)padded_count);
+    if (padded_count == 0) return MACKO_OK;
+    if (!values || !deltas || !workspace) return fail(MACKO_ERR_INVALID_ARGUMENT, "null output or workspace");
+    if (!aligned(deltas, 4) || !aligned(workspace, 8))
+        return fail(MACKO_ERR_MISALIGNED, "deltas needs 4-, workspace 8-byte alignment");
+    if (workspace_bytes < macko_compress_workspace_bytes(padded_count))
+        return fail(MACKO_ERR_WORKSPACE, "workspace has %lld bytes, %lld needed", (long long)workspace_bytes,
+                    (long long)macko_compress_workspace_bytes(padded_count));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (rows > 0) {
+        const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+        compress_rows_int8_kernel<true><<<grid, kThreads, 0, s>>>(
+            static_cast<const signed char *>(dense), (int)rows, (int)cols, aligned(dense, 8), nullptr, row_indices,
+            static_cast<signed char *>(values), static_cast<unsigned char *>(workspace), (int)padded_count);
+        st = launch_error("int8 compress emit launch");
+        if (st != MACKO_OK) return st;
+    }
+    const int groups = (int)(padded_count / 8);
+    pack_kernel<signed char><<<(groups + 255) / 256, 256, 0, s>>>(
+        static_cast<const uint2 *>(workspace), row_indices, (int)rows, groups,
+        static_cast<unsigned *>(deltas), static_cast<signed char *>(values));
+    return launch_error("int8 pack launch");
 }
 
 int macko_compress_overflow(uint32_t *count, void *stream)
@@ -469,7 +627,7 @@ int macko_compress_emit_static(const void *dense, int64_t rows, int64_t cols, co
         if (st != MACKO_OK) return st;
     }
     const int groups = (int)(padded_count / 8);
-    pack_kernel<<<(groups + 255) / 256, 256, 0, s>>>(
+    pack_kernel<unsigned short><<<(groups + 255) / 256, 256, 0, s>>>(
         reinterpret_cast<const uint2 *>(scratch), row_indices, (int)rows, groups,
         static_cast<unsigned *>(deltas), static_cast<unsigned short *>(values));
     return launch_error("pack (static scratch) launch");

@@ -50,10 +50,13 @@ constexpr int kXPadBack = 160;       // zero fp16 slots after x[cols-1]  (> 8 * 
 // acc += fp16(low or high half of vword) * fp16(low half of xbits): the sm_100 mixed-precision FMA
 // (exact fp16 product accumulated in fp32, round to nearest); the halves are split inside the asm so
 // that no repacking instructions are needed around it.
-template <int HALF, bool BF = false>
+// Value types of the stored elements (x and y follow: fp16 for fp16 and int8 values, bf16 for bf16 values)
+constexpr int kF16 = 0, kBF16 = 1, kI8 = 2;
+
+template <int HALF, int VT = kF16>
 __device__ __forceinline__ float fma_h(float acc, unsigned vword, unsigned xbits)
 {
-    if (BF) {
+    if (VT == kBF16) {
         if (HALF)
             asm("{.reg .b16 l,h,xl,xh; mov.b32 {l,h}, %1; mov.b32 {xl,xh}, %2; fma.rn.f32.bf16 %0, h, xl, %0;}"
                 : "+f"(acc) : "r"(vword), "r"(xbits));
@@ -72,17 +75,53 @@ __device__ __forceinline__ float fma_h(float acc, unsigned vword, unsigned xbits
 }
 
 // 16-bit storage type <-> fp32 for the y epilogue (fp16 or bf16 bits in an unsigned short)
-template <bool BF>
+template <int VT>
 __device__ __forceinline__ unsigned short to_bits16(float f)
 {
-    if (BF) return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+    if (VT == kBF16) return __bfloat16_as_ushort(__float2bfloat16_rn(f));
     return __half_as_ushort(__float2half_rn(f));
 }
-template <bool BF>
+template <int VT>
 __device__ __forceinline__ float from_bits16(unsigned short b)
 {
-    if (BF) return __bfloat162float(__ushort_as_bfloat16(b));
+    if (VT == kBF16) return __bfloat162float(__ushort_as_bfloat16(b));
     return __half2float(__ushort_as_half(b));
+}
+
+// Four signed bytes -> their exact fp16 values, as two f16x2 words (elements 0,1 and 2,3): flip the sign bit
+// (byte + 128 as an unsigned byte), put every byte under the exponent of 1024.0 (0x64xx = 1024 + byte) and
+// subtract 1152.0: one permute and one packed subtraction per pair.
+__device__ __forceinline__ void bytes_to_f16x2(unsigned w, unsigned &lo, unsigned &hi)
+{
+    const unsigned u = w ^ 0x80808080u;
+    unsigned a = __byte_perm(u, 0x64646464u, 0x4140);
+    unsigned b = __byte_perm(u, 0x64646464u, 0x4342);
+    asm("sub.f16x2 %0, %0, %1;" : "+r"(a) : "r"(0x64806480u));
+    asm("sub.f16x2 %0, %0, %1;" : "+r"(b) : "r"(0x64806480u));
+    lo = a;
+    hi = b;
+}
+
+__device__ __forceinline__ uint2 ldg_stream_v2(const uint2 *p)
+{
+    uint2 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+    return r;
+}
+
+// Zero the deltas and the int8 values (in v.x, v.y) of one 8-element unit outside element range [lo, hi).
+__device__ __forceinline__ void mask_unit_bytes(uint4 &v, unsigned &w, int lo, int hi)
+{
+    lo = min(max(lo, 0), kGroup);
+    hi = min(max(hi, 0), kGroup);
+    unsigned m = lo >= kGroup ? 0u : (0xffffffffu << (4 * lo));
+    if (hi < kGroup) m &= ~(0xffffffffu << (4 * hi));
+    w &= m;
+    unsigned keep[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) keep[j >> 2] |= (((m >> (4 * j)) & 1u) * 0xffu) << (8 * (j & 3));
+    v.x &= keep[0];
+    v.y &= keep[1];
 }
 
 // acc += fp16(half VH of vword) * fp16(half XH of xword)
@@ -237,11 +276,13 @@ struct Extra {
 //       so one vector load gathers a column of all of them.
 // PLAN  rows come from a plan: virtual rows (begin, length, starting column, destination) sorted by length;
 //       the segments of a long row leave fp32 partial sums that the last one to finish adds up in segment order
-// BF    values, x and y are bfloat16 instead of fp16 (same buffers, same decode; fp32 accumulation either way)
+// VT    value type: kF16; kBF16 (values, x and y are bfloat16: same buffers, same decode); kI8 (values are
+//       signed bytes, 8 per 64-bit load, x and y fp16: the reference's int8 variant, kernels.cuh:127-216);
+//       fp32 accumulation in every case
 // EARLY the caller has declared the matrix immutable: the first matrix loads are issued before the wait for the
 //       previous kernel of the stream and before x is staged (a separate instantiation, so that the default
 //       launch keeps the simpler code: wait, stage x, then walk the rows)
-template <int L, int NPAIR, bool XS, bool PEER, int BV = 1, bool PLAN = false, bool BF = false, bool EARLY = false>
+template <int L, int NPAIR, bool XS, bool PEER, int BV = 1, bool PLAN = false, int VT = kF16, bool EARLY = false>
 __global__ void __launch_bounds__(kThreads, 2)
 spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ deltas,
             const int *__restrict__ ri, const __half *__restrict__ x, __half *__restrict__ y,
@@ -250,7 +291,7 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
 {
     static_assert(BV == 1 || (XS && !PEER), "batched products gather from shared memory and have no scatter epilogue");
     static_assert(!PLAN || (XS && !PEER && BV == 1), "planned launches are built for the single-vector product with x in shared memory");
-    static_assert(!BF || (!PEER && BV == 1 && !PLAN), "bfloat16 is built for the plain single-vector product");
+    static_assert(VT == kF16 || (!PEER && BV == 1 && !PLAN), "bfloat16 and int8 values are built for the plain single-vector product");
     static_assert(!EARLY || BV == 1, "early matrix loads are built for the single-vector product");
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int STEP = kGroup * L;   // elements per group per sub-step
@@ -412,8 +453,8 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                             ystage[my_row - cta_row_lo] = __float2half_rn(alpha * total);   // delivered in bulk at the end
                         } else {
                             float r = alpha * total;
-                            if (beta != 0.f) r += beta * from_bits16<BF>(y16[my_row]);
-                            y16[my_row] = to_bits16<BF>(r);
+                            if (beta != 0.f) r += beta * from_bits16<VT>(y16[my_row]);
+                            y16[my_row] = to_bits16<VT>(r);
                         }
                     }
                     acc0 = acc1 = acc2 = acc3 = 0.f;
@@ -498,7 +539,13 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 v[s] = make_uint4(0u, 0u, 0u, 0u);
                 w[s] = 0u;
                 if (s * STEP < rem0) {
-                    v[s] = ldg_stream_v4(vp + s * L);
+                    if constexpr (VT == kI8) {
+                        const uint2 t = ldg_stream_v2(reinterpret_cast<const uint2 *>(values) + (ord0 >> 3) + s * L);
+                        v[s].x = t.x;
+                        v[s].y = t.y;
+                    } else {
+                        v[s] = ldg_stream_v4(vp + s * L);
+                    }
                     w[s] = ldg_stream_u32(dp + s * L);
                 }
             }
@@ -540,7 +587,10 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
 #pragma unroll
             for (int hs = 0; hs < 2; ++hs) {
                 const int s = 2 * p + hs;
-                if (straddle & (1u << s)) mask_unit(v[s], w[s], (s == 0) ? lo0 : 0, rem0 - s * STEP);
+                if (straddle & (1u << s)) {
+                    if constexpr (VT == kI8) mask_unit_bytes(v[s], w[s], (s == 0) ? lo0 : 0, rem0 - s * STEP);
+                    else mask_unit(v[s], w[s], (s == 0) ? lo0 : 0, rem0 - s * STEP);
+                }
                 const unsigned ev = w[s] & 0x0f0f0f0fu;
                 const unsigned od = (w[s] >> 4) & 0x0f0f0f0fu;
                 const unsigned pe = ev * 0x02020202u + 0x0c080400u;
@@ -566,7 +616,12 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                 const unsigned sel = hs ? 0x0100u : 0x0001u;
                 const unsigned a0 = min(__dp2a_lo(ex, sel, run) + (unsigned)(2 * L * s), a_max);   // keeps malformed input inside the padded x
                 run = __dp2a_lo(g, sel, run);
-                const unsigned *vw = reinterpret_cast<const unsigned *>(&v[s]);
+                unsigned vconv[4];   // int8: the unit's 8 values as four f16x2 words
+                if constexpr (VT == kI8) {
+                    bytes_to_f16x2(v[s].x, vconv[0], vconv[1]);
+                    bytes_to_f16x2(v[s].y, vconv[2], vconv[3]);
+                }
+                const unsigned *vw = (VT == kI8) ? vconv : reinterpret_cast<const unsigned *>(&v[s]);
                 if constexpr (BV > 1) {
                     const int ab = x_base + (int)a0 * BV;
                     auto element_pair = [&](auto jt) {
@@ -612,14 +667,14 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
                         xe[3] = gather(add_byte<3>(ce[hs], (int)a0));
                         xo[3] = gather(add_byte<3>(co[hs], (int)a0));
                     }
-                    acc0 = fma_h<0, BF>(acc0, vw[0], xe[0]);
-                    acc1 = fma_h<1, BF>(acc1, vw[0], xo[0]);
-                    acc2 = fma_h<0, BF>(acc2, vw[1], xe[1]);
-                    acc3 = fma_h<1, BF>(acc3, vw[1], xo[1]);
-                    acc0 = fma_h<0, BF>(acc0, vw[2], xe[2]);
-                    acc1 = fma_h<1, BF>(acc1, vw[2], xo[2]);
-                    acc2 = fma_h<0, BF>(acc2, vw[3], xe[3]);
-                    acc3 = fma_h<1, BF>(acc3, vw[3], xo[3]);
+                    acc0 = fma_h<0, VT == kBF16 ? kBF16 : kF16>(acc0, vw[0], xe[0]);
+                    acc1 = fma_h<1, VT == kBF16 ? kBF16 : kF16>(acc1, vw[0], xo[0]);
+                    acc2 = fma_h<0, VT == kBF16 ? kBF16 : kF16>(acc2, vw[1], xe[1]);
+                    acc3 = fma_h<1, VT == kBF16 ? kBF16 : kF16>(acc3, vw[1], xo[1]);
+                    acc0 = fma_h<0, VT == kBF16 ? kBF16 : kF16>(acc0, vw[2], xe[2]);
+                    acc1 = fma_h<1, VT == kBF16 ? kBF16 : kF16>(acc1, vw[2], xo[2]);
+                    acc2 = fma_h<0, VT == kBF16 ? kBF16 : kF16>(acc2, vw[3], xe[3]);
+                    acc3 = fma_h<1, VT == kBF16 ? kBF16 : kF16>(acc3, vw[3], xo[3]);
                 }
             }
         }
@@ -770,27 +825,27 @@ bool use_pdl()
     return on;
 }
 
-template <int L, int NPAIR, bool XS, bool PEER, int BV, bool PLAN, bool BF, bool EARLY>
+template <int L, int NPAIR, bool XS, bool PEER, int BV, bool PLAN, int VT, bool EARLY>
 int launch_variant(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
                    const void *x, void *y, float alpha, float beta, cudaStream_t stream,
                    const DeviceInfo &dev, int ctas_per_sm, const Peers &peers, int batch, const Extra &extra);
 
 // The instantiation with or without early matrix loads, by the immutable-matrix flag of the call.
-template <int L, int NPAIR, bool XS, bool PEER = false, int BV = 1, bool PLAN = false, bool BF = false>
+template <int L, int NPAIR, bool XS, bool PEER = false, int BV = 1, bool PLAN = false, int VT = kF16>
 int launch(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
            const void *x, void *y, float alpha, float beta, cudaStream_t stream,
            const DeviceInfo &dev, int ctas_per_sm, const Peers &peers = Peers{}, int batch = 1, const Extra &extra = Extra{})
 {
     if constexpr (BV == 1) {
         if (extra.flags & MACKO_SPMV_MATRIX_IMMUTABLE)
-            return launch_variant<L, NPAIR, XS, PEER, BV, PLAN, BF, true>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta,
+            return launch_variant<L, NPAIR, XS, PEER, BV, PLAN, VT, true>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta,
                                                                          stream, dev, ctas_per_sm, peers, batch, extra);
     }
-    return launch_variant<L, NPAIR, XS, PEER, BV, PLAN, BF, false>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta,
+    return launch_variant<L, NPAIR, XS, PEER, BV, PLAN, VT, false>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta,
                                                                   stream, dev, ctas_per_sm, peers, batch, extra);
 }
 
-template <int L, int NPAIR, bool XS, bool PEER, int BV, bool PLAN, bool BF, bool EARLY>
+template <int L, int NPAIR, bool XS, bool PEER, int BV, bool PLAN, int VT, bool EARLY>
 int launch_variant(const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
                    const void *x, void *y, float alpha, float beta, cudaStream_t stream,
                    const DeviceInfo &dev, int ctas_per_sm, const Peers &peers, int batch, const Extra &extra)
@@ -801,7 +856,7 @@ int launch_variant(const void *values, const void *deltas, const int32_t *ri, in
     if (smem > (size_t)dev.max_smem_optin)
         return fail(MACKO_ERR_INVALID_ARGUMENT, "the launch needs %lld bytes of shared memory, the device offers %d (cols=%d)",
                     (long long)smem, dev.max_smem_optin, cols);
-    auto kernel = spmv_kernel<L, NPAIR, XS, PEER, BV, PLAN, BF, EARLY>;
+    auto kernel = spmv_kernel<L, NPAIR, XS, PEER, BV, PLAN, VT, EARLY>;
     if (smem > 48 * 1024) {
         // Idempotent and cheap; set on every call so that every device is covered.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -841,29 +896,29 @@ int launch_variant(const void *values, const void *deltas, const int32_t *ri, in
     return MACKO_OK;
 }
 
-template <int L, bool XS, bool BF>
+template <int L, bool XS, int VT>
 int launch_d(int D, const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
              const void *x, void *y, float alpha, float beta, cudaStream_t stream,
              const DeviceInfo &dev, int ctas_per_sm, const Extra &extra)
 {
     switch (D) {
-        case 2: return launch<L, 1, XS, false, 1, false, BF>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
-        case 4: return launch<L, 2, XS, false, 1, false, BF>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
-        case 6: return launch<L, 3, XS, false, 1, false, BF>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
+        case 2: return launch<L, 1, XS, false, 1, false, VT>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
+        case 4: return launch<L, 2, XS, false, 1, false, VT>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
+        case 6: return launch<L, 3, XS, false, 1, false, VT>(values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, Peers{}, 1, extra);
         default: return fail(MACKO_ERR_INVALID_ARGUMENT, "steps_in_flight must be 2, 4 or 6 (got %d)", D);
     }
 }
 
-template <bool XS, bool BF = false>
+template <bool XS, int VT = kF16>
 int launch_l(int L, int D, const void *values, const void *deltas, const int32_t *ri, int rows, int cols, long long padded,
              const void *x, void *y, float alpha, float beta, cudaStream_t stream,
              const DeviceInfo &dev, int ctas_per_sm, const Extra &extra = Extra{})
 {
     switch (L) {
-        case 4: return launch_d<4, XS, BF>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
-        case 8: return launch_d<8, XS, BF>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
-        case 16: return launch_d<16, XS, BF>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
-        case 32: return launch_d<32, XS, BF>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
+        case 4: return launch_d<4, XS, VT>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
+        case 8: return launch_d<8, XS, VT>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
+        case 16: return launch_d<16, XS, VT>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
+        case 32: return launch_d<32, XS, VT>(D, values, deltas, ri, rows, cols, padded, x, y, alpha, beta, stream, dev, ctas_per_sm, extra);
         default: return fail(MACKO_ERR_INVALID_ARGUMENT, "lanes_per_row must be 4, 8, 16 or 32 (got %d)", L);
     }
 }
@@ -950,7 +1005,7 @@ int check_flags(uint32_t flags)
 }
 
 // The default launch: shape from the chooser, x in shared memory when it fits.
-template <bool BF>
+template <int VT>
 int spmv_default(const void *values, const void *deltas, const int32_t *row_indices,
                  int64_t rows, int64_t cols, int64_t padded_count,
                  const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream)
@@ -972,8 +1027,8 @@ int spmv_default(const void *values, const void *deltas, const int32_t *row_indi
     Extra extra = {};
     extra.flags = flags;
     if (xs)
-        return launch_l<true, BF>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
-    return launch_l<false, BF>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
+        return launch_l<true, VT>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
+    return launch_l<false, VT>(L, D, values, deltas, row_indices, (int)rows, (int)cols, padded_count, x, y, alpha, beta, s, *dev, 0, extra);
 }
 
 }  // namespace
@@ -1010,21 +1065,28 @@ int macko_spmv_fp16(const void *values, const void *deltas, const int32_t *row_i
                     int64_t rows, int64_t cols, int64_t padded_count,
                     const void *x, void *y, float alpha, float beta, void *stream)
 {
-    return macko::spmv_default<false>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, 0u, stream);
+    return macko::spmv_default<macko::kF16>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, 0u, stream);
 }
 
 int macko_spmv_fp16_ex(const void *values, const void *deltas, const int32_t *row_indices,
                        int64_t rows, int64_t cols, int64_t padded_count,
                        const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream)
 {
-    return macko::spmv_default<false>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, flags, stream);
+    return macko::spmv_default<macko::kF16>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, flags, stream);
 }
 
 int macko_spmv_bf16(const void *values, const void *deltas, const int32_t *row_indices,
                     int64_t rows, int64_t cols, int64_t padded_count,
                     const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream)
 {
-    return macko::spmv_default<true>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, flags, stream);
+    return macko::spmv_default<macko::kBF16>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, flags, stream);
+}
+
+int macko_spmv_int8(const void *values, const void *deltas, const int32_t *row_indices,
+                    int64_t rows, int64_t cols, int64_t padded_count,
+                    const void *x, void *y, float alpha, float beta, uint32_t flags, void *stream)
+{
+    return macko::spmv_default<macko::kI8>(values, deltas, row_indices, rows, cols, padded_count, x, y, alpha, beta, flags, stream);
 }
 
 int macko_spmv_fp16_planned(const void *values, const void *deltas, const int32_t *row_indices,

@@ -26,8 +26,10 @@ void check_status(int status, const char *what)
 void check_compressed(const at::Tensor &values, const at::Tensor &deltas, const at::Tensor &ri,
                       int64_t rows, int64_t cols)
 {
-    // fp16 is the reference's type; bfloat16 runs the same layout through the bf16 kernel
-    TORCH_CHECK(values.dtype() == at::kHalf || values.dtype() == at::kBFloat16, "M must be torch.half");
+    // fp16 is the reference's type; bfloat16 runs the same layout through the bf16 kernel, int8 the reference's
+    // int8 variant of the format (values one byte each, vectors fp16)
+    TORCH_CHECK(values.dtype() == at::kHalf || values.dtype() == at::kBFloat16 || values.dtype() == at::kChar,
+                "M must be torch.half");
     TORCH_CHECK(deltas.dtype() == at::kByte, "M_deltas must be torch.uint8");
     TORCH_CHECK(ri.dtype() == at::kInt, "M_row_indices must be torch.int32");
     TORCH_CHECK(values.is_cuda() && deltas.is_cuda() && ri.is_cuda(), "compressed buffers must be CUDA tensors");
@@ -46,15 +48,20 @@ at::Tensor multiply_flags(const at::Tensor &values, const at::Tensor &deltas, co
                           int64_t rows, int64_t cols, const at::Tensor &V, uint32_t flags)
 {
     check_compressed(values, deltas, ri, rows, cols);
-    TORCH_CHECK(V.dtype() == values.dtype(), "V must be torch.half");
+    const bool int8 = values.dtype() == at::kChar;
+    TORCH_CHECK(V.dtype() == (int8 ? at::ScalarType::Half : values.scalar_type()), "V must be torch.half");
     TORCH_CHECK(V.is_cuda() && V.device() == values.device(), "V must be on the device of M");
     TORCH_CHECK(V.is_contiguous(), "V must be contiguous");
     TORCH_CHECK(V.dim() == 1 && V.size(0) == cols, "V must have shape [M_cols]");
 
     const c10::cuda::CUDAGuard guard(values.device());
-    at::Tensor y = at::empty({rows}, values.options());
+    at::Tensor y = at::empty({rows}, V.options());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
-    if (values.dtype() == at::kBFloat16)
+    if (int8)
+        check_status(macko_spmv_int8(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                     values.numel(), V.data_ptr(), y.data_ptr(), 1.0f, 0.0f, flags, stream),
+                     "macko_spmv_int8");
+    else if (values.dtype() == at::kBFloat16)
         check_status(macko_spmv_bf16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
                                      values.numel(), V.data_ptr(), y.data_ptr(), 1.0f, 0.0f, flags, stream),
                      "macko_spmv_bf16");
@@ -137,14 +144,19 @@ void multiply_out_cuda(const at::Tensor &values, const at::Tensor &deltas, const
                        int64_t rows, int64_t cols, const at::Tensor &V, at::Tensor y, double alpha, double beta)
 {
     check_compressed(values, deltas, ri, rows, cols);
-    TORCH_CHECK(V.dtype() == values.dtype() && y.dtype() == values.dtype(), "V and y must be torch.half");
+    const bool int8 = values.dtype() == at::kChar;
+    TORCH_CHECK(V.dtype() == (int8 ? at::ScalarType::Half : values.scalar_type()) && y.dtype() == V.dtype(), "V and y must be torch.half");
     TORCH_CHECK(V.is_cuda() && V.device() == values.device() && y.device() == values.device(),
                 "V and y must be on the device of M");
     TORCH_CHECK(V.is_contiguous() && y.is_contiguous(), "V and y must be contiguous");
     TORCH_CHECK(V.dim() == 1 && V.size(0) == cols && y.dim() == 1 && y.size(0) == rows, "bad vector shapes");
     const c10::cuda::CUDAGuard guard(values.device());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
-    if (values.dtype() == at::kBFloat16)
+    if (int8)
+        check_status(macko_spmv_int8(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                     values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, 0u, stream),
+                     "macko_spmv_int8");
+    else if (values.dtype() == at::kBFloat16)
         check_status(macko_spmv_bf16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
                                      values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, 0u, stream),
                      "macko_spmv_bf16");
@@ -159,14 +171,19 @@ void multiply_ex_cuda(const at::Tensor &values, const at::Tensor &deltas, const 
                       int64_t rows, int64_t cols, const at::Tensor &V, at::Tensor y, double alpha, double beta, int64_t flags)
 {
     check_compressed(values, deltas, ri, rows, cols);
-    TORCH_CHECK(V.dtype() == values.dtype() && y.dtype() == values.dtype(), "V and y must be torch.half");
+    const bool int8 = values.dtype() == at::kChar;
+    TORCH_CHECK(V.dtype() == (int8 ? at::ScalarType::Half : values.scalar_type()) && y.dtype() == V.dtype(), "V and y must be torch.half");
     TORCH_CHECK(V.is_cuda() && V.device() == values.device() && y.device() == values.device(),
                 "V and y must be on the device of M");
     TORCH_CHECK(V.is_contiguous() && y.is_contiguous(), "V and y must be contiguous");
     TORCH_CHECK(V.dim() == 1 && V.size(0) == cols && y.dim() == 1 && y.size(0) == rows, "bad vector shapes");
     const c10::cuda::CUDAGuard guard(values.device());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
-    if (values.dtype() == at::kBFloat16)
+    if (int8)
+        check_status(macko_spmv_int8(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
+                                     values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, (uint32_t)flags, stream),
+                     "macko_spmv_int8");
+    else if (values.dtype() == at::kBFloat16)
         check_status(macko_spmv_bf16(values.data_ptr(), deltas.data_ptr(), ri.data_ptr<int32_t>(), rows, cols,
                                      values.numel(), V.data_ptr(), y.data_ptr(), (float)alpha, (float)beta, (uint32_t)flags, stream),
                      "macko_spmv_bf16");
@@ -198,6 +215,7 @@ at::Tensor decompress_cuda(const at::Tensor &values, const at::Tensor &deltas, c
                            int64_t rows, int64_t cols)
 {
     check_compressed(values, deltas, ri, rows, cols);
+    TORCH_CHECK(values.dtype() != at::kChar, "decompress is built for 16-bit values");
     const c10::cuda::CUDAGuard guard(values.device());
     at::Tensor dense = at::empty({rows, cols}, values.options());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
@@ -210,7 +228,7 @@ at::Tensor decompress_cuda(const at::Tensor &values, const at::Tensor &deltas, c
 std::tuple<at::Tensor, at::Tensor, at::Tensor> compress_cuda(const at::Tensor &M)
 {
     TORCH_CHECK(M.is_cuda(), "M must be a CUDA tensor");
-    TORCH_CHECK(M.dtype() == at::kHalf || M.dtype() == at::kBFloat16, "M must be torch.half");
+    TORCH_CHECK(M.dtype() == at::kHalf || M.dtype() == at::kBFloat16 || M.dtype() == at::kChar, "M must be torch.half");
     TORCH_CHECK(M.dim() == 2, "M must be a matrix");
     TORCH_CHECK(M.is_contiguous(), "M must be contiguous");
     const int64_t rows = M.size(0), cols = M.size(1);
@@ -218,15 +236,24 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> compress_cuda(const at::Tensor &M
     const c10::cuda::CUDAGuard guard(M.device());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
     at::Tensor ri = at::empty({rows + 1}, M.options().dtype(at::kInt));
-    check_status(macko_compress_count(M.data_ptr(), rows, cols, ri.data_ptr<int32_t>(), stream),
-                 "macko_compress_count");
+    const bool int8 = M.dtype() == at::kChar;
+    if (int8)
+        check_status(macko_compress_count_int8(M.data_ptr(), rows, cols, ri.data_ptr<int32_t>(), stream),
+                     "macko_compress_count_int8");
+    else
+        check_status(macko_compress_count(M.data_ptr(), rows, cols, ri.data_ptr<int32_t>(), stream),
+                     "macko_compress_count");
     const int64_t n = ri[rows].item<int32_t>();  // the one device->host read that sizes the outputs
     const int64_t padded = (n + 7) / 8 * 8;
     at::Tensor values = at::empty({padded}, M.options());
     at::Tensor deltas = at::empty({padded / 2}, M.options().dtype(at::kByte));
     const int64_t ws_bytes = macko_compress_workspace_bytes(padded);
     at::Tensor ws = at::empty({ws_bytes}, M.options().dtype(at::kByte));
-    if (M.dtype() == at::kBFloat16)
+    if (int8)
+        check_status(macko_compress_emit_int8(M.data_ptr(), rows, cols, ri.data_ptr<int32_t>(), padded,
+                                              values.data_ptr(), deltas.data_ptr(), ws.data_ptr(), ws_bytes, stream),
+                     "macko_compress_emit_int8");
+    else if (M.dtype() == at::kBFloat16)
         check_status(macko_compress_emit_bf16(M.data_ptr(), rows, cols, ri.data_ptr<int32_t>(), padded,
                                               values.data_ptr(), deltas.data_ptr(), ws.data_ptr(), ws_bytes, stream),
                      "macko_compress_emit_bf16");

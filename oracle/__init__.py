@@ -22,6 +22,7 @@ _REF_KERNEL_PATH = os.path.join(_HERE, "_ref", "libref_kernel.so")
 
 _u16p = ctypes.POINTER(ctypes.c_uint16)
 _u8p = ctypes.POINTER(ctypes.c_uint8)
+_i8p = ctypes.POINTER(ctypes.c_int8)
 _i32p = ctypes.POINTER(ctypes.c_int32)
 _f64p = ctypes.POINTER(ctypes.c_double)
 _i64 = ctypes.c_int64
@@ -70,6 +71,10 @@ def _load():
         lib.oracle_spmv_fp16.argtypes = [_u16p, _u8p, _i32p, _i64, _i64, _u16p, _f64p, _u16p, _f64p]
         lib.oracle_dense_matvec_fp16.restype = None
         lib.oracle_dense_matvec_fp16.argtypes = [_u16p, _i64, _i64, _u16p, _f64p]
+        lib.oracle_compress_int8.restype = _i64
+        lib.oracle_compress_int8.argtypes = [_i8p, _i64, _i64, _i8p, _u8p, _i32p, ctypes.POINTER(_i64)]
+        lib.oracle_spmv_int8.restype = None
+        lib.oracle_spmv_int8.argtypes = [_i8p, _u8p, _i32p, _i64, _i64, _u16p, _f64p, _f64p]
         lib.oracle_num_threads.restype = ctypes.c_int
         _lib = lib
     return _lib
@@ -88,6 +93,11 @@ def _load_ref():
         ref.ref_compress_fp16.argtypes = [
             _u16p, ctypes.c_int, ctypes.c_int,
             ctypes.POINTER(_u16p), ctypes.POINTER(_u8p), ctypes.POINTER(_i32p), ctypes.POINTER(_i64),
+        ]
+        ref.ref_compress_int8.restype = _i64
+        ref.ref_compress_int8.argtypes = [
+            _i8p, ctypes.c_int, ctypes.c_int,
+            ctypes.POINTER(_i8p), ctypes.POINTER(_u8p), ctypes.POINTER(_i32p), ctypes.POINTER(_i64),
         ]
         ref.ref_free.restype = None
         ref.ref_free.argtypes = [ctypes.c_void_p]
@@ -204,6 +214,61 @@ def spmv(compressed, x):
                          ri.ctypes.data_as(_i32p), rows, cols, x.ctypes.data_as(_u16p),
                          y64.ctypes.data_as(_f64p), yh.ctypes.data_as(_u16p), l1.ctypes.data_as(_f64p))
     return y64, yh, l1
+
+
+def compress_int8(dense):
+    """Oracle compress of an int8 matrix: (values i8[P], deltas u8[P/2], row_indices i32[R+1], R, C)."""
+    lib = _load()
+    dense = np.ascontiguousarray(dense, dtype=np.int8)
+    assert dense.ndim == 2
+    rows, cols = dense.shape
+    bound = ((rows * cols + 7) // 8) * 8 + 8
+    values = np.empty(bound, dtype=np.int8)
+    deltas = np.empty(bound // 2, dtype=np.uint8)
+    ri = np.empty(rows + 1, dtype=np.int32)
+    n = _i64(0)
+    padded = int(lib.oracle_compress_int8(dense.ctypes.data_as(_i8p), rows, cols, values.ctypes.data_as(_i8p),
+                                          deltas.ctypes.data_as(_u8p), ri.ctypes.data_as(_i32p), ctypes.byref(n)))
+    return values[:padded].copy(), deltas[: padded // 2].copy(), ri, rows, cols
+
+
+def ref_compress_int8(dense):
+    """The reference's own ``compress_rows_int8_cpu`` (cpu_compressor.cuh:75-117), same 5-tuple."""
+    ref = _load_ref()
+    dense = np.ascontiguousarray(dense, dtype=np.int8)
+    rows, cols = dense.shape
+    v, d, r = _i8p(), _u8p(), _i32p()
+    n = _i64(0)
+    padded = int(ref.ref_compress_int8(dense.ctypes.data_as(_i8p), rows, cols,
+                                       ctypes.byref(v), ctypes.byref(d), ctypes.byref(r), ctypes.byref(n)))
+    try:
+        if padded > 0:
+            values = np.ctypeslib.as_array(v, shape=(padded,)).copy()
+            deltas = np.ctypeslib.as_array(d, shape=(padded // 2,)).copy()
+        else:
+            values = np.empty(0, dtype=np.int8)
+            deltas = np.empty(0, dtype=np.uint8)
+        ri = np.ctypeslib.as_array(r, shape=(rows + 1,)).copy()
+    finally:
+        ref.ref_free(v)
+        ref.ref_free(d)
+        ref.ref_free(r)
+    return values, deltas, ri, rows, cols
+
+
+def spmv_int8(compressed, x):
+    """(y float64[R], row L1 mass float64[R]) for int8 values and fp16 x (bit patterns)."""
+    lib = _load()
+    values, deltas, ri, rows, cols = compressed
+    values = np.ascontiguousarray(values, dtype=np.int8)
+    deltas = np.ascontiguousarray(deltas, dtype=np.uint8)
+    ri = np.ascontiguousarray(ri, dtype=np.int32)
+    x = _as_u16(x)
+    y64 = np.empty(rows, dtype=np.float64)
+    l1 = np.empty(rows, dtype=np.float64)
+    lib.oracle_spmv_int8(values.ctypes.data_as(_i8p), deltas.ctypes.data_as(_u8p), ri.ctypes.data_as(_i32p),
+                         rows, cols, x.ctypes.data_as(_u16p), y64.ctypes.data_as(_f64p), l1.ctypes.data_as(_f64p))
+    return y64, l1
 
 
 def bf16_bits_to_f64(bits) -> np.ndarray:

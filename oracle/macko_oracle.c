@@ -253,6 +253,74 @@ void oracle_spmv_fp16(const uint16_t *values, const uint8_t *deltas,
     }
 }
 
+/* ---- int8 values (restating src/macko_spmv/cuda/cpu_compressor.cuh:75-117 and kernels.cuh:127-216) ----
+ * Same delta packing and row offsets; values are one signed byte each. The int8 encoder of the reference
+ * has no trailing clean-up: a run of zeros at the end of a row still leaves a pad (value 0, delta 15) for
+ * every full 16 of them (cpu_compressor.cuh:88-111), and the leftover count is simply dropped. Parity is
+ * pinned against the compiled reference encoder (oracle/_ref) and the fixtures generated from it; the
+ * reference has no known-answer test for int8. */
+int64_t oracle_compress_int8(const int8_t *dense, int64_t rows, int64_t cols,
+                             int8_t *values, uint8_t *deltas, int32_t *row_indices, int64_t *n_out)
+{
+    row_indices[0] = 0;
+    int64_t total = 0;
+    for (int64_t r = 0; r < rows; ++r) {
+        const int8_t *row = dense + r * cols;
+        int64_t n = 0, prev = -1;
+        for (int64_t c = 0; c < cols; ++c)
+            if (row[c] != 0) { n += ((c - prev - 1) >> 4) + 1; prev = c; }
+        n += (cols - 1 - prev) >> 4;   /* pads inside the trailing zeros stay */
+        total += n;
+        row_indices[r + 1] = (int32_t)total;
+    }
+    int64_t padded = ((total + 7) / 8) * 8;
+    memset(values, 0, (size_t)padded);
+    memset(deltas, 0, (size_t)(padded / 2));
+    for (int64_t r = 0; r < rows; ++r) {
+        const int8_t *row = dense + r * cols;
+        int64_t k = row_indices[r];
+        int64_t prev = -1;
+        for (int64_t c = 0; c <= cols; ++c) {
+            if (c < cols && row[c] == 0) continue;
+            for (int64_t p = prev + 16; p < c; p += 16) {   /* pads on columns prev+16, prev+32, ... (value 0) */
+                values[k] = 0;
+                deltas[k >> 1] |= (uint8_t)(15u << (4 * (k & 1)));
+                ++k;
+            }
+            if (c == cols) break;
+            values[k] = row[c];
+            deltas[k >> 1] |= (uint8_t)(((c - prev - 1) & 15) << (4 * (k & 1)));
+            ++k;
+            prev = c;
+        }
+    }
+    if (n_out) *n_out = total;
+    return padded;
+}
+
+/* y = M x for int8 values and fp16 x: exact products accumulated in double, and the row L1 mass. */
+void oracle_spmv_int8(const int8_t *values, const uint8_t *deltas, const int32_t *row_indices,
+                      int64_t rows, int64_t cols, const uint16_t *x, double *y_f64, double *l1)
+{
+#ifdef _OPENMP
+#pragma omp parallel for schedule(dynamic, 64)
+#endif
+    for (int64_t r = 0; r < rows; ++r) {
+        int64_t col = -1;
+        double acc = 0.0, mag = 0.0;
+        for (int64_t k = row_indices[r]; k < row_indices[r + 1]; ++k) {
+            int d = (deltas[k >> 1] >> (4 * (k & 1))) & 15;
+            col += d + 1;
+            int64_t c = col >= cols ? cols - 1 : col;   /* kernels.cuh:196-197 clamps */
+            double p = (double)values[k] * (double)h2f(x[c]);
+            acc += p;
+            mag += p < 0 ? -p : p;
+        }
+        if (y_f64) y_f64[r] = acc;
+        if (l1) l1[r] = mag;
+    }
+}
+
 /* Dense fp32-accumulated matvec of an fp16 matrix (the "dense M@V" tier). */
 void oracle_dense_matvec_fp16(const uint16_t *dense, int64_t rows, int64_t cols,
                               const uint16_t *x, double *y_f64)

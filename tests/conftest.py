@@ -65,3 +65,20 @@ def reference_cases():
         }
         for n in names
     ]
+
+
+@pytest.fixture(scope="session")
+def reference_cases_int8():
+    """Fixtures produced by the compiled reference int8 encoder (tests/golden/make_golden.py)."""
+    z = np.load(os.path.join(GOLDEN_DIR, "reference_cases_int8.npz"))
+    names = sorted({k.split("/")[0] for k in z.files})
+    return [
+        {
+            "name": n,
+            "dense": z[f"{n}/dense"],
+            "values": z[f"{n}/values"],
+            "deltas": z[f"{n}/deltas"],
+            "row_indices": z[f"{n}/row_indices"],
+        }
+        for n in names
+    ]

@@ -62,8 +62,43 @@ def cases():
     return out
 
 
+def cases_int8():
+    """Inputs for the reference's int8 encoder (cpu_compressor.cuh:75-117): random matrices, exact zero gaps
+    around the pad boundary at the start, in the middle and at the END of a row (that encoder keeps trailing
+    pads), and every tail residue mod 8."""
+    rng = np.random.default_rng(20251126)
+    out = {}
+    for (r, c) in [(1, 1), (1, 15), (1, 16), (1, 33), (9, 1), (3, 32), (5, 33), (17, 100), (12, 257), (7, 515)]:
+        for d in (0.0, 0.02, 0.1, 0.5, 1.0):
+            m = rng.integers(-128, 128, size=(r, c)).astype(np.int8)
+            m[rng.random((r, c)) > d] = 0
+            out[f"i8_rand_{r}x{c}_d{int(d * 100):03d}"] = m
+    for gap in (14, 15, 16, 17, 31, 32, 33, 48, 255, 256):
+        row = np.zeros((3, gap + 40), dtype=np.int8)
+        row[0, gap] = 5                         # leading gap, then trailing zeros
+        row[1, 3] = -7
+        row[1, 3 + gap + 1] = 9                 # interior gap
+        row[2, 0] = 1                           # only trailing zeros: gap + 39 of them
+        out[f"i8_gap_{gap}"] = row
+    for n in range(0, 17):
+        m = np.zeros((3, 16), dtype=np.int8)
+        m.reshape(-1)[:n] = -3
+        out[f"i8_tail_{n}"] = m
+    return out
+
+
 def main():
     assert oracle.have_reference(), "build oracle/_ref first (make -C oracle)"
+    data8 = {}
+    for name, dense in cases_int8().items():
+        v, d, ri, r, c = oracle.ref_compress_int8(dense)
+        data8[f"{name}/dense"] = dense
+        data8[f"{name}/values"] = v
+        data8[f"{name}/deltas"] = d
+        data8[f"{name}/row_indices"] = ri
+    path8 = os.path.join(HERE, "reference_cases_int8.npz")
+    np.savez_compressed(path8, **data8)
+    print(f"wrote {path8}: {len(data8) // 4} cases, {os.path.getsize(path8)} bytes")
     data = {}
     for name, dense in cases().items():
         v, d, ri, r, c = oracle.ref_compress(dense)

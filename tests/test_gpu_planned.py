@@ -381,3 +381,66 @@ def test_deferred_exchange_all_ranks_on_one_gpu(world, split):
                 assert torch.equal(ys[r][:rows].view(torch.int16), full.view(torch.int16)), (rows, cols, r, rep)
                 assert int(fl[r][world + 2]) == 0, "a wait gave up"
                 assert all(int(fl[r][p]) == rep + 1 for p in range(world))
+
+
+# ---------------------------------------------------------------- int8 values
+
+def _assert_int8_buffers(comp, exp, what=""):
+    assert comp[0].dtype == torch.int8 and comp[1].dtype == torch.uint8 and comp[2].dtype == torch.int32
+    assert np.array_equal(comp[0].cpu().numpy(), exp[0]), f"values differ {what}"
+    assert np.array_equal(comp[1].cpu().numpy(), exp[1]), f"deltas differ {what}"
+    assert np.array_equal(comp[2].cpu().numpy(), exp[2]), f"row_indices differ {what}"
+
+
+def test_int8_compress_fixtures_from_compiled_reference(reference_cases_int8):
+    lib = cabi.load()
+    stream = _stream()
+    for c in reference_cases_int8:
+        M = torch.from_numpy(c["dense"]).cuda()
+        exp = (c["values"], c["deltas"], c["row_indices"])
+        _assert_int8_buffers(macko_spmv.compress(M), exp, c["name"] + " (python api)")
+        # the C ABI with raw pointers, at a 1-byte-aligned address as well (scalar load path)
+        rows, cols = M.shape
+        buf = torch.zeros(rows * cols + 1, dtype=torch.int8, device="cuda")
+        Mo = buf[1:].view(rows, cols)
+        Mo.copy_(M)
+        ri = torch.empty(rows + 1, dtype=torch.int32, device="cuda")
+        cabi.check(lib, lib.macko_compress_count_int8(Mo.data_ptr(), rows, cols, ri.data_ptr(), stream))
+        P = (int(ri[rows].item()) + 7) // 8 * 8
+        values = torch.empty(P, dtype=torch.int8, device="cuda")
+        deltas = torch.empty(P // 2, dtype=torch.uint8, device="cuda")
+        ws = torch.empty(max(P, 8), dtype=torch.uint8, device="cuda")
+        cabi.check(lib, lib.macko_compress_emit_int8(Mo.data_ptr(), rows, cols, ri.data_ptr(), P, values.data_ptr(),
+                                                     deltas.data_ptr(), ws.data_ptr(), ws.numel(), stream))
+        _assert_int8_buffers((values, deltas, ri), exp, c["name"] + " (c abi, unaligned)")
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (5, 33), (33, 257), (257, 1000), (1000, 1), (7, 30000), (4096, 4096), (11008, 4096)])
+def test_int8_compress_and_multiply_against_oracle(shape):
+    rows, cols = shape
+    g = torch.Generator().manual_seed(rows * 131 + cols)
+    for dens in (0.0, 0.01, 0.1, 0.5, 1.0):
+        M = torch.randint(-128, 128, (rows, cols), generator=g, dtype=torch.int8)
+        M[torch.rand(rows, cols, generator=g) > dens] = 0
+        exp = oracle.compress_int8(M.numpy())
+        comp = macko_spmv.compress(M.cuda())
+        _assert_int8_buffers(comp, exp, f"{shape} d={dens}")
+        x = (torch.randn(cols, generator=g) * 0.1).half()
+        y64, l1 = oracle.spmv_int8(exp, _u16(x))
+        for name, cm in (("default", comp), ("frozen", macko_spmv.freeze(comp))):
+            y = macko_spmv.multiply(cm, x.cuda())
+            assert y.dtype == torch.float16 and y.shape == (rows,)
+            got = y.float().cpu().numpy().astype(np.float64)
+            err = np.abs(got - y64)
+            assert np.all(err <= MAX_ABS_FACTOR * l1 + 1e-12), f"{shape} d={dens} {name}: worst {float((err / (l1 + 1e-30)).max()):.3e} of L1"
+            nrm = np.linalg.norm(y64)
+            assert np.linalg.norm(got - y64) <= REL_L2 * nrm + 1e-12, f"{shape} d={dens} {name}"
+    # alpha / beta and the error behaviour of the other entry points
+    y0 = torch.ones(rows, dtype=torch.float16, device="cuda")
+    torch.ops.macko_spmv.multiply_out(comp[0], comp[1], comp[2], rows, cols, x.cuda(), y0, 0.5, 2.0)
+    ref = macko_spmv.multiply(comp, x.cuda()).float() * 0.5 + 2.0
+    assert torch.allclose(y0.float(), ref, rtol=2e-3, atol=2e-3 * float(ref.abs().max()) + 1e-3)
+    with pytest.raises(RuntimeError, match="torch.half"):
+        macko_spmv.multiply(comp, x.cuda().float())
+    with pytest.raises(RuntimeError):
+        macko_spmv.decompress(comp)
