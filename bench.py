@@ -42,10 +42,11 @@ import torch  # noqa: E402
 METRIC = "spmv_us_sum_llama7b_sweep"
 UNIT = "us"
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per algorithmic byte of the SpMV kernel, from the profiler capture of one 32000x4096, 50 %
-# matrix (profiles/spmv_kernel_32000x4096_d50.md: dram read + write over algorithmic bytes). The step's
-# traffic is that ratio times its algorithmic bytes: traffic grows in proportion to the stored elements.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.04
+# DRAM bytes per algorithmic byte of one step, from the profiler's launch list of this program
+# (profiles/spmv_sweep_launches.md: dram__bytes_read.sum + dram__bytes_write.sum of the 36 launches of a step
+# over the step's algorithmic bytes; 24 steps of the capture agree within 0.1 %). A single 32000x4096 product
+# at 50 % reads 1.04 (profiles/spmv_kernel_32000x4096_d50.md).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.012
 WORKLOAD = ("llama2-7b linear-layer sweep: shapes 4096x4096, 11008x4096, 4096x11008, 32000x4096 x densities "
             "0.1..0.9, per-row magnitude pruning; one step = one SpMV per matrix (36)")
 
@@ -931,8 +932,9 @@ def run_own_arm(args):
                 "bound": "hbm", "achieved": round(achieved, 1), "peak": peak_gbs, "unit": "GB/s",
                 "frac": round(achieved / peak_gbs, 4),
                 "traffic": int(step_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE) if world == 1 else None,
-                "traffic_source": "dram bytes per algorithmic byte (1.04) from the profiler capture of one 32000x4096 50 % product "
-                                  "(profiles/spmv_kernel_32000x4096_d50.md), scaled by the step's algorithmic bytes; not measured in this run",
+                "traffic_source": "dram bytes per algorithmic byte (1.012) of the 36 launches of a step in the profiler's launch "
+                                  "list of this program (profiles/spmv_sweep_launches.md), times the step's algorithmic bytes; "
+                                  "not measured in this run",
                 "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_step_per_gpu": step_bytes,
                 "large_matrix_frac_min": round(min(large_fracs), 4) if large_fracs else None,
                 "large_matrix_frac_max": round(max(large_fracs), 4) if large_fracs else None,

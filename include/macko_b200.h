@@ -356,6 +356,30 @@ int macko_peer_wait_limited(uint32_t *local_flags, int world, uint32_t spin_limi
 int macko_peer_forward(void *const *peer_y, int64_t row_offset, int64_t rows, uint32_t *const *peer_flags,
                        int rank, int world, void *stream);
 
+/*
+ * Decode helpers: the steps between the products of a batch-1 decode step of a Llama-architecture
+ * transformer (fp16 everywhere, fp32 arithmetic inside). The reference has no such code of its own: its
+ * tokens/s are measured on a Hugging Face model whose projections are swapped for MACKO layers
+ * (python_scripts/util_run_pruned_llm.py:102-133, 159-207), and the model code around them is the
+ * library's. All three launch with programmatic stream serialization, like the products.
+ *
+ * macko_decode_add_rmsnorm: x[i] += pending[0][i] + ... + pending[n_pending-1][i] (row p of `pending` starts at
+ *   pending + p * pending_stride elements; fp32 sum in that order, rounded once; n_pending may be 0), then
+ *   out[i] = x[i] * rsqrt(mean(x^2) + eps) * weight[i]. x is updated in place; out must not alias x.
+ * macko_decode_rope_attention: qkv = [3][heads][head_dim] (q, k, v of the new token); rotary embedding
+ *   (rotate-half convention, tables [max_len][head_dim] with both halves equal) of q and k at *position
+ *   (an int64 on the device, clamped into [0, max_len)), k and v stored into row *position of the caches
+ *   ([heads][max_len][head_dim]), out[heads][head_dim] = softmax(q k^T / sqrt(head_dim)) v over cache rows
+ *   0..*position. One CTA per head: built for the contexts of a benchmark (hundreds of positions), not for
+ *   long ones. head_dim 64, 128 or 256.
+ * macko_decode_silu_mul: out[i] = silu(gate_up[i]) * gate_up[n + i], i < n.
+ */
+int macko_decode_add_rmsnorm(void *x, const void *pending, int n_pending, int64_t pending_stride, const void *weight,
+                             void *out, int64_t n, float eps, void *stream);
+int macko_decode_rope_attention(const void *qkv, const void *cos_table, const void *sin_table, const int64_t *position,
+                                void *k_cache, void *v_cache, void *out, int heads, int head_dim, int max_len, void *stream);
+int macko_decode_silu_mul(const void *gate_up, void *out, int64_t n, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -96,6 +96,21 @@ def _multiply_planned_fake(M_values, M_deltas, M_row_indices, M_rows, M_cols, pl
     return torch.empty((M_rows,), device=M_values.device, dtype=M_values.dtype)
 
 
+@torch.library.register_fake("macko_spmv::add_rmsnorm")
+def _add_rmsnorm_fake(x, pending, weight, eps):
+    return torch.empty_like(x)
+
+
+@torch.library.register_fake("macko_spmv::rope_attention")
+def _rope_attention_fake(qkv, cos_table, sin_table, position, k_cache, v_cache):
+    return qkv.new_empty((qkv.numel() // 3,))
+
+
+@torch.library.register_fake("macko_spmv::silu_mul")
+def _silu_mul_fake(gate_up):
+    return gate_up.new_empty((gate_up.shape[0] // 2,))
+
+
 def move_to_device(compressed, device):
     """Move the three buffers of a compressed matrix (src/macko_spmv/__init__.py:110-117)."""
     return (

@@ -21,7 +21,7 @@ LIB_CORE = os.path.join(PKG_DIR, "libmacko_b200.so")
 LIB_TORCH = os.path.join(PKG_DIR, "_torch_ops.so")
 BENCH_CLI = os.path.join(PKG_DIR, "macko_bench")
 
-CUDA_SOURCES = ["common.cu", "spmv.cu", "compress.cu", "decompress.cu", "plan.cu"]
+CUDA_SOURCES = ["common.cu", "spmv.cu", "compress.cu", "decompress.cu", "plan.cu", "decode_glue.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
@@ -106,7 +106,7 @@ def build_cli(force: bool = False, verbose: bool = False) -> str:
     if not force and _newer(BENCH_CLI, [src, LIB_CORE, os.path.join(INCLUDE, "macko_b200.h"), __file__]):
         return BENCH_CLI
     _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-I", INCLUDE, src, "-o", BENCH_CLI,
-          "-L", PKG_DIR, "-l:libmacko_b200.so", "-lcublas", "-Xlinker", "-rpath=$ORIGIN"], verbose)
+          "-L", PKG_DIR, "-l:libmacko_b200.so", "-lcublas", "-lcusparse", "-Xlinker", "-rpath=$ORIGIN"], verbose)
     return BENCH_CLI
 
 

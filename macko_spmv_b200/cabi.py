@@ -70,6 +70,9 @@ SIGNATURES = {
     "macko_spmv_fp16_scatter_ex": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _int, _int, _u32, _u32, _vp]),
     "macko_peer_wait_limited": (_int, [_vp, _int, _u32, _vp]),
     "macko_peer_forward": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp]),
+    "macko_decode_add_rmsnorm": (_int, [_vp, _vp, _int, _i64, _vp, _vp, _i64, _f, _vp]),
+    "macko_decode_rope_attention": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _vp]),
+    "macko_decode_silu_mul": (_int, [_vp, _vp, _i64, _vp]),
 }
 
 

@@ -4,16 +4,20 @@
 //
 //   macko_bench <bits_per_value> <rows> <cols> <warmup> <timing> <flush> <debug> <kernel_id> <seed> <density>
 //
-// kernel_id 7 is the MACKO SpMV (here: macko_spmv_fp16 of this library), 1 and 2 are cuBLAS GemmEx with
-// fp16 and fp32 accumulation on the dense matrix, 0 is the fp32 cuBLAS GEMV every result is checked against.
-// Only 16 bits per value exist in this library. The protocol is the reference's: one checked run, warm-up,
-// 100 launches timed on the host for the launch cost, then `timing` launches timed one by one with CUDA
-// events, each after an optional flush of L2 (a memset of twice its size); the matrix holds exactly
-// floor(density * rows * cols) non-zeros with values k/100, k in [-50, 50] \ {0}, placed by sequential
-// selection sampling. The data is generated by this program's own generator (seeded), compressed on the
-// GPU through the C ABI, and the last line is
+// kernel_id 7 is the MACKO SpMV (here: macko_spmv_fp16 of this library), 8 the int8 MACKO SpMV (bits_per_value 8:
+// macko_spmv_int8), 1 and 2 are cuBLAS GemmEx with fp16 and fp32 accumulation on the dense matrix, 3 is cuSPARSE
+// SpMM on a CSR copy (CUSPARSE_SPMM_CSR_ALG1, fp16 values, fp32 compute: c_benchmarking/benchmark.cu:76-90,
+// utils.cuh:405-462), 0 is the fp32 cuBLAS GEMV every result is checked against. The protocol is the
+// reference's: one checked run, warm-up, 100 launches timed on the host for the launch cost, then `timing`
+// launches timed one by one with CUDA events, each after an optional flush of L2 (a memset of twice its size).
+// The data follows the reference's generator call for call (c_benchmarking/utils.cuh:464-519 after
+// srand(seed), benchmark.cu:138): every matrix entry drawn as (rand() % 101 - 50) / 100 (bits 16) or
+// rand() % 101 - 50 (bits 8) until non-zero, the vector likewise, then exactly int(density * rows * cols)
+// entries kept by sequential selection sampling with rand(); so a run sees the matrix the reference CLI sees
+// for the same arguments on the same C library. It is compressed on the GPU through the C ABI, and the last line is
 //   Final results:\t<bits>\t<rows>\t<cols>\t<kernel_id>\t<density>\t<mean us>\t<dense Gflops>\t<sparse Gflops>
 #include <cublas_v2.h>
+#include <cusparse.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -48,6 +52,15 @@ namespace {
         }                                                                                                  \
     } while (0)
 
+#define CUSPARSE_OK(expr)                                                                                  \
+    do {                                                                                                   \
+        cusparseStatus_t s_ = (expr);                                                                      \
+        if (s_ != CUSPARSE_STATUS_SUCCESS) {                                                               \
+            std::cerr << "cuSPARSE error " << (int)s_ << " at " << __FILE__ << ":" << __LINE__ << std::endl; \
+            std::exit(2);                                                                                  \
+        }                                                                                                  \
+    } while (0)
+
 #define MACKO_CALL(expr)                                                                                   \
     do {                                                                                                   \
         int st_ = (expr);                                                                                  \
@@ -62,24 +75,15 @@ struct Args {
     float density = 1.f;
 };
 
-struct Rng {   // splitmix64
-    uint64_t s;
-    explicit Rng(uint64_t seed) : s(seed * 0x9e3779b97f4a7c15ull + 0x1234567ull) {}
-    uint64_t next()
-    {
-        uint64_t z = (s += 0x9e3779b97f4a7c15ull);
-        z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
-        z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
-        return z ^ (z >> 31);
-    }
-    uint64_t below(uint64_t n) { return (uint64_t)(((unsigned __int128)next() * n) >> 64); }
-    float value()   // k / 100 with k in [-50, 50], never 0
-    {
-        int k = (int)below(100) - 50;
-        if (k >= 0) ++k;
-        return (float)k / 100.f;
-    }
-};
+// One draw of the reference generator: uniform over {-50, ..., 50} \ {0} by rejection (utils.cuh:464-489)
+int draw_nonzero()
+{
+    int k;
+    do {
+        k = rand() % 101 - 50;
+    } while (k == 0);
+    return k;
+}
 
 struct Data {
     Args a;
@@ -91,26 +95,34 @@ struct Data {
     int32_t *ri_d = nullptr;
     int64_t padded = 0;
     bool last_output_is_half = true;
+    // cuSPARSE CSR copy of the dense fp16 matrix (kernel id 3), built on first use
+    cusparseHandle_t sp = nullptr;
+    cusparseSpMatDescr_t sp_a = nullptr;
+    cusparseDnMatDescr_t dn_a = nullptr, dn_b = nullptr, dn_c = nullptr;
+    void *sp_buffer = nullptr;
+    const float sp_alpha = 1.f, sp_beta = 0.f;
 
     explicit Data(const Args &args) : a(args)
     {
         n = (size_t)a.rows * a.cols;
-        Rng rng((uint64_t)a.seed);
+        srand((unsigned)a.seed);
         m32.resize(n);
         v32.resize(a.cols);
-        // exactly floor(density * n) non-zeros: keep element i with probability (still to keep) / (still to see)
-        uint64_t keep = (uint64_t)((double)a.density * (double)n);
-        uint64_t left = n;
-        for (size_t i = 0; i < n; ++i, --left) {
-            const float val = rng.value();
-            if (rng.below(left) < keep) {
-                m32[i] = val;
-                --keep;
-            } else {
+        // bits 8: integer values, as the int8 matrix needs them
+        for (size_t i = 0; i < n; ++i) m32[i] = a.bits == 16 ? float(draw_nonzero()) / 100 : float(draw_nonzero());
+        for (int i = 0; i < a.cols; ++i) v32[i] = float(draw_nonzero()) / 100;
+        // exactly int(density * n) non-zeros survive: entry i stays with probability (still to keep) / (still to see)
+        int ones_to_sample = int(a.density * float((int)n));
+        int zeros_to_sample = (int)n - ones_to_sample;
+        for (size_t i = 0; i < n; ++i) {
+            const bool is_one = (rand() % (ones_to_sample + zeros_to_sample)) < ones_to_sample;
+            if (!is_one) {
                 m32[i] = 0.f;
+                --zeros_to_sample;
+            } else {
+                --ones_to_sample;
             }
         }
-        for (int i = 0; i < a.cols; ++i) v32[i] = rng.value();
         std::vector<__half> m16(n), v16(a.cols);
         for (size_t i = 0; i < n; ++i) m16[i] = __float2half(m32[i]);
         for (int i = 0; i < a.cols; ++i) v16[i] = __float2half(v32[i]);
@@ -131,6 +143,27 @@ struct Data {
 
         // MACKO buffers from the GPU compressor
         CUDA_OK(cudaMalloc(&ri_d, ((size_t)a.rows + 1) * sizeof(int32_t)));
+        if (a.bits == 8) {
+            std::vector<int8_t> m8(n);
+            for (size_t i = 0; i < n; ++i) m8[i] = (int8_t)m32[i];
+            int8_t *m8_d = nullptr;
+            CUDA_OK(cudaMalloc(&m8_d, std::max<size_t>(n, 8)));
+            CUDA_OK(cudaMemcpy(m8_d, m8.data(), n, cudaMemcpyHostToDevice));
+            MACKO_CALL(macko_compress_count_int8(m8_d, a.rows, a.cols, ri_d, nullptr));
+            int32_t stored8 = 0;
+            CUDA_OK(cudaMemcpy(&stored8, ri_d + a.rows, sizeof(int32_t), cudaMemcpyDeviceToHost));
+            padded = ((int64_t)stored8 + 7) / 8 * 8;
+            void *ws8 = nullptr;
+            CUDA_OK(cudaMalloc(&values_d, std::max<int64_t>(padded, 16)));
+            CUDA_OK(cudaMalloc(&deltas_d, std::max<int64_t>(padded / 2, 4)));
+            CUDA_OK(cudaMalloc(&ws8, std::max<int64_t>(macko_compress_workspace_bytes(padded), 8)));
+            MACKO_CALL(macko_compress_emit_int8(m8_d, a.rows, a.cols, ri_d, padded, values_d, deltas_d, ws8,
+                                                macko_compress_workspace_bytes(padded), nullptr));
+            CUDA_OK(cudaDeviceSynchronize());
+            CUDA_OK(cudaFree(ws8));
+            CUDA_OK(cudaFree(m8_d));
+            return;
+        }
         MACKO_CALL(macko_compress_count(m16_d, a.rows, a.cols, ri_d, nullptr));
         int32_t stored = 0;
         CUDA_OK(cudaMemcpy(&stored, ri_d + a.rows, sizeof(int32_t), cudaMemcpyDeviceToHost));
@@ -145,14 +178,44 @@ struct Data {
         CUDA_OK(cudaFree(ws));
     }
 
+    // CSR copy of the dense fp16 matrix through cuSPARSE's own dense-to-sparse conversion, and the SpMM buffer
+    void setup_cusparse()
+    {
+        if (sp) return;
+        int *row_ptr = nullptr, *col_ind = nullptr;
+        __half *csr_val = nullptr;
+        CUDA_OK(cudaMalloc(&row_ptr, sizeof(int) * ((size_t)a.rows + 1)));
+        CUSPARSE_OK(cusparseCreate(&sp));
+        CUSPARSE_OK(cusparseCreateDnMat(&dn_a, a.rows, a.cols, a.cols, m16_d, CUDA_R_16F, CUSPARSE_ORDER_ROW));
+        CUSPARSE_OK(cusparseCreateDnMat(&dn_b, a.cols, 1, a.cols, v16_d, CUDA_R_16F, CUSPARSE_ORDER_COL));
+        CUSPARSE_OK(cusparseCreateDnMat(&dn_c, a.rows, 1, a.rows, y16_d, CUDA_R_16F, CUSPARSE_ORDER_COL));
+        CUSPARSE_OK(cusparseCreateCsr(&sp_a, a.rows, a.cols, 0, row_ptr, nullptr, nullptr, CUSPARSE_INDEX_32I, CUSPARSE_INDEX_32I,
+                                      CUSPARSE_INDEX_BASE_ZERO, CUDA_R_16F));
+        size_t bytes = 0;
+        void *tmp = nullptr;
+        CUSPARSE_OK(cusparseDenseToSparse_bufferSize(sp, dn_a, sp_a, CUSPARSE_DENSETOSPARSE_ALG_DEFAULT, &bytes));
+        CUDA_OK(cudaMalloc(&tmp, std::max<size_t>(bytes, 8)));
+        CUSPARSE_OK(cusparseDenseToSparse_analysis(sp, dn_a, sp_a, CUSPARSE_DENSETOSPARSE_ALG_DEFAULT, tmp));
+        int64_t r = 0, c = 0, nnz = 0;
+        CUSPARSE_OK(cusparseSpMatGetSize(sp_a, &r, &c, &nnz));
+        CUDA_OK(cudaMalloc(&col_ind, std::max<int64_t>(nnz, 1) * sizeof(int)));
+        CUDA_OK(cudaMalloc(&csr_val, std::max<int64_t>(nnz, 1) * sizeof(__half)));
+        CUSPARSE_OK(cusparseCsrSetPointers(sp_a, row_ptr, col_ind, csr_val));
+        CUSPARSE_OK(cusparseDenseToSparse_convert(sp, dn_a, sp_a, CUSPARSE_DENSETOSPARSE_ALG_DEFAULT, tmp));
+        CUDA_OK(cudaFree(tmp));
+        CUSPARSE_OK(cusparseSpMM_bufferSize(sp, CUSPARSE_OPERATION_NON_TRANSPOSE, CUSPARSE_OPERATION_NON_TRANSPOSE, &sp_alpha, sp_a,
+                                            dn_b, &sp_beta, dn_c, CUDA_R_32F, CUSPARSE_SPMM_CSR_ALG1, &bytes));
+        CUDA_OK(cudaMalloc(&sp_buffer, std::max<size_t>(bytes, 8)));
+    }
+
     double dense_gflops(double us) const { return 2.0 * a.rows * a.cols / (us * 1e3); }
     double sparse_gflops(double us) const { return 2.0 * a.rows * a.cols * a.density / (us * 1e3); }
     double dense_bandwidth(double us) const { return 2.0 * ((double)n + a.rows + a.cols) / (us * 1e3); }
     double compressed_bandwidth(double us) const
     {
-        return (2.5 * padded + 4.0 * (a.rows + 1) + 2.0 * a.cols + 2.0 * a.rows) / (us * 1e3);
+        return ((a.bits == 8 ? 1.5 : 2.5) * padded + 4.0 * (a.rows + 1) + 2.0 * a.cols + 2.0 * a.rows) / (us * 1e3);
     }
-    double effective_density() const { return (2.5 * padded + 4.0 * a.cols) / (2.0 * (double)n); }
+    double effective_density() const { return ((a.bits == 8 ? 1.5 : 2.5) * padded + 4.0 * a.cols) / ((a.bits == 8 ? 1.0 : 2.0) * (double)n); }
 };
 
 void run(int kernel_id, Data &d, cudaStream_t stream, cublasHandle_t handle)
@@ -180,11 +243,22 @@ void run(int kernel_id, Data &d, cudaStream_t stream, cublasHandle_t handle)
                                    CUBLAS_GEMM_DEFAULT));
             break;
         }
+        case 3:     // cuSPARSE SpMM on the CSR copy
+            d.setup_cusparse();
+            CUSPARSE_OK(cusparseSetStream(d.sp, stream));
+            CUSPARSE_OK(cusparseSpMM(d.sp, CUSPARSE_OPERATION_NON_TRANSPOSE, CUSPARSE_OPERATION_NON_TRANSPOSE, &d.sp_alpha, d.sp_a,
+                                     d.dn_b, &d.sp_beta, d.dn_c, CUDA_R_32F, CUSPARSE_SPMM_CSR_ALG1, d.sp_buffer));
+            break;
         case 7:     // MACKO SpMV
+            if (a.bits != 16) { std::cerr << "NO KERNEL (kernel id 7 takes 16 bits per value)" << std::endl; std::exit(1); }
             MACKO_CALL(macko_spmv_fp16(d.values_d, d.deltas_d, d.ri_d, a.rows, a.cols, d.padded, d.v16_d, d.y16_d, 1.f, 0.f, stream));
             break;
+        case 8:     // MACKO SpMV, int8 values
+            if (a.bits != 8) { std::cerr << "NO KERNEL (kernel id 8 takes 8 bits per value)" << std::endl; std::exit(1); }
+            MACKO_CALL(macko_spmv_int8(d.values_d, d.deltas_d, d.ri_d, a.rows, a.cols, d.padded, d.v16_d, d.y16_d, 1.f, 0.f, 0u, stream));
+            break;
         default:
-            std::cerr << "NO KERNEL (this library has kernel ids 0, 1, 2 and 7)" << std::endl;
+            std::cerr << "NO KERNEL (this library has kernel ids 0, 1, 2, 3, 7 and 8)" << std::endl;
             std::exit(1);
     }
 }
@@ -214,8 +288,12 @@ int main(int argc, char **argv)
         std::cerr << "Error: Invalid arguments: " << e.what() << std::endl;
         return 1;
     }
-    if (a.bits != 16) {
-        std::cerr << "Only 16 bits per value are built in this library." << std::endl;
+    if (a.bits != 16 && a.bits != 8) {
+        std::cerr << "Only 16 and 8 bits per value are built in this library." << std::endl;
+        return 1;
+    }
+    if ((int64_t)a.rows * a.cols >= (1LL << 31)) {
+        std::cerr << "Error: Invalid arguments: rows * cols must stay below 2^31" << std::endl;
         return 1;
     }
     if (a.rows <= 0 || a.cols <= 0 || a.timing <= 0 || a.warmup < 0 || a.density < 0.f || a.density > 1.f) {

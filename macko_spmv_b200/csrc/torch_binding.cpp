@@ -264,6 +264,67 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> compress_cuda(const at::Tensor &M
     return std::make_tuple(values, deltas, ri);
 }
 
+// ---- decode helpers (macko_decode_*): the steps between the products of a batch-1 decode step ------------
+
+void check_half_vec(const at::Tensor &t, const char *name)
+{
+    TORCH_CHECK(t.is_cuda() && t.dtype() == at::kHalf && t.is_contiguous(), name, " must be a contiguous CUDA fp16 tensor");
+}
+
+// x[n] += rows of pending[k, n] (k may be 0); returns rmsnorm(x) * weight
+at::Tensor add_rmsnorm_cuda(at::Tensor x, const at::Tensor &pending, const at::Tensor &weight, double eps)
+{
+    check_half_vec(x, "x");
+    check_half_vec(weight, "weight");
+    check_half_vec(pending, "pending");
+    TORCH_CHECK(x.dim() == 1 && weight.dim() == 1 && weight.size(0) == x.size(0), "x and weight must be vectors of one length");
+    TORCH_CHECK(pending.dim() == 2 && (pending.size(0) == 0 || pending.size(1) == x.size(0)), "pending must be [k, n]");
+    TORCH_CHECK(pending.device() == x.device() && weight.device() == x.device(), "tensors on different devices");
+    const c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor out = at::empty_like(x);
+    const int k = (int)pending.size(0);
+    check_status(macko_decode_add_rmsnorm(x.data_ptr(), k ? pending.data_ptr() : nullptr, k, x.size(0), weight.data_ptr(),
+                                          out.data_ptr(), x.size(0), (float)eps, c10::cuda::getCurrentCUDAStream()),
+                 "macko_decode_add_rmsnorm");
+    return out;
+}
+
+at::Tensor rope_attention_cuda(const at::Tensor &qkv, const at::Tensor &cos_table, const at::Tensor &sin_table,
+                               const at::Tensor &position, at::Tensor k_cache, at::Tensor v_cache)
+{
+    check_half_vec(qkv, "qkv");
+    check_half_vec(cos_table, "cos_table");
+    check_half_vec(sin_table, "sin_table");
+    check_half_vec(k_cache, "k_cache");
+    check_half_vec(v_cache, "v_cache");
+    TORCH_CHECK(position.is_cuda() && position.dtype() == at::kLong && position.numel() == 1, "position must be one int64 on the device");
+    TORCH_CHECK(k_cache.dim() >= 3 && k_cache.sizes() == v_cache.sizes(), "caches must be [..., heads, max_len, head_dim]");
+    const int64_t hd = k_cache.size(-1), max_len = k_cache.size(-2), heads = k_cache.numel() / (hd * max_len);
+    TORCH_CHECK(qkv.numel() == 3 * heads * hd, "qkv must hold q, k and v of ", heads, " heads");
+    TORCH_CHECK(cos_table.dim() == 2 && cos_table.size(1) == hd && cos_table.size(0) >= max_len && sin_table.sizes() == cos_table.sizes(),
+                "cos/sin tables must be [>= max_len, head_dim]");
+    const c10::cuda::CUDAGuard guard(qkv.device());
+    at::Tensor out = at::empty({heads * hd}, qkv.options());
+    check_status(macko_decode_rope_attention(qkv.data_ptr(), cos_table.data_ptr(), sin_table.data_ptr(),
+                                             position.data_ptr<int64_t>(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                             (int)heads, (int)hd, (int)max_len, c10::cuda::getCurrentCUDAStream()),
+                 "macko_decode_rope_attention");
+    return out;
+}
+
+at::Tensor silu_mul_cuda(const at::Tensor &gate_up)
+{
+    check_half_vec(gate_up, "gate_up");
+    TORCH_CHECK(gate_up.dim() == 1 && gate_up.size(0) % 2 == 0, "gate_up must be a vector of 2n elements");
+    const c10::cuda::CUDAGuard guard(gate_up.device());
+    const int64_t n = gate_up.size(0) / 2;
+    at::Tensor out = at::empty({n}, gate_up.options());
+    if (n > 0)
+        check_status(macko_decode_silu_mul(gate_up.data_ptr(), out.data_ptr(), n, c10::cuda::getCurrentCUDAStream()),
+                     "macko_decode_silu_mul");
+    return out;
+}
+
 }  // namespace
 
 TORCH_LIBRARY(macko_spmv, m)
@@ -280,6 +341,10 @@ TORCH_LIBRARY(macko_spmv, m)
     m.def("plan_build(Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, int padded_count, int segment_elements) -> (Tensor, Tensor)");
     m.def("multiply_planned(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor plan, "
           "int virtual_rows, int segment_elements, int split_rows, Tensor V, bool frozen) -> Tensor");
+    m.def("add_rmsnorm(Tensor(a!) x, Tensor pending, Tensor weight, float eps) -> Tensor");
+    m.def("rope_attention(Tensor qkv, Tensor cos_table, Tensor sin_table, Tensor position, Tensor(a!) k_cache, "
+          "Tensor(b!) v_cache) -> Tensor");
+    m.def("silu_mul(Tensor gate_up) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
@@ -293,4 +358,7 @@ TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
     m.impl("multiply_frozen", &multiply_frozen_cuda);
     m.impl("plan_build", &plan_build_cuda);
     m.impl("multiply_planned", &multiply_planned_cuda);
+    m.impl("add_rmsnorm", &add_rmsnorm_cuda);
+    m.impl("rope_attention", &rope_attention_cuda);
+    m.impl("silu_mul", &silu_mul_cuda);
 }
