@@ -1078,8 +1078,8 @@ def main():
     ap.add_argument("--no-skewed", action="store_true", help="skip the skewed-density matrices")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-architecture decode figures")
     ap.add_argument("--decode-layers", type=int, default=32)
-    ap.add_argument("--decode-prompt", type=int, default=16)
-    ap.add_argument("--decode-tokens", type=int, default=48)
+    ap.add_argument("--decode-prompt", type=int, default=128)
+    ap.add_argument("--decode-tokens", type=int, default=256)
     ap.add_argument("--exchange", choices=["peer", "peer-fused", "nccl"], default="peer",
                     help="N > 1: how the y slices are exchanged: peer stores by a forward kernel beside the next products, "
                          "peer stores from the tail of the product kernel, or NCCL all-gather")

@@ -150,95 +150,162 @@ silu_mul_kernel(const __half *__restrict__ gu, __half *__restrict__ out, int n)
 
 constexpr int kAttnWarps = 8;
 
-// One CTA per head; head_dim = 32 * VPL, lane l holds dimensions l, l + 32, ... (the rotary partner of dimension d,
-// d +- head_dim / 2, then sits in the same lane). qkv is [3][heads][head_dim] (q, k, v of the new token, not yet
-// rotated), cos/sin tables are [max_len][head_dim] with both halves equal, caches are [heads][max_len][head_dim].
-// Warp w takes cache rows w, w + 8, ... with an online softmax of its own; the eight partial results are merged
-// at the end. Row pos (the new token) is taken from shared memory, not from the cache rows written here.
+// VPL consecutive fp16 values as one load or store (4, 8 or 16 bytes).
+template <int VPL> struct HalfVec;
+template <> struct HalfVec<2> { using type = unsigned; };
+template <> struct HalfVec<4> { using type = uint2; };
+template <> struct HalfVec<8> { using type = uint4; };
+
 template <int VPL>
-__global__ void __launch_bounds__(kAttnWarps * 32)
+__device__ __forceinline__ void unpack_halfs(const typename HalfVec<VPL>::type &raw, float (&f)[VPL])
+{
+    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+    for (int j = 0; j < VPL / 2; ++j) {
+        const float2 t = __half22float2(h[j]);
+        f[2 * j] = t.x;
+        f[2 * j + 1] = t.y;
+    }
+}
+
+template <int VPL>
+__device__ __forceinline__ typename HalfVec<VPL>::type pack_halfs(const float (&f)[VPL])
+{
+    typename HalfVec<VPL>::type raw;
+    __half2 *h = reinterpret_cast<__half2 *>(&raw);
+#pragma unroll
+    for (int j = 0; j < VPL / 2; ++j) h[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+    return raw;
+}
+
+__device__ __forceinline__ float ld_cluster_f32(const float *local, unsigned cta_rank)
+{
+    // the same shared-memory variable in the CTA `cta_rank` of this cluster
+    unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(cta_rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void cluster_barrier()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// One thread-block cluster per head (1, 2, 4 or 8 CTAs, by how many heads there are: the cluster's CTAs have
+// consecutive blockIdx.x); head_dim = 32 * VPL, lane l holds dimensions VPL*l .. VPL*l + VPL - 1, so a cache row
+// is one vector load per lane and the rotary partner of a dimension, head_dim / 2 away, sits 16 lanes away.
+// qkv is [3][heads][head_dim] (q, k, v of the new token, not yet rotated), the cos/sin tables are
+// [max_len][head_dim] with both halves equal, the caches are [heads][max_len][head_dim]. Every CTA rotates q and
+// k for itself; the first one of the cluster stores k and v into cache row pos. The warps of the cluster take
+// cache rows round robin, four rows per iteration with all loads issued first, each warp with an online softmax
+// of its own (row pos, the new token, comes from shared memory, not from the cache row written here); the warps
+// of a CTA are merged through shared memory, the CTAs of the cluster through distributed shared memory by the
+// first CTA. Every thread of every CTA reaches both cluster barriers: there is no early exit.
+template <int VPL>
+__global__ void __launch_bounds__(kAttnWarps * 32, 1)
 rope_attention_kernel(const __half *__restrict__ qkv, const __half *__restrict__ cos_table, const __half *__restrict__ sin_table,
                       const long long *__restrict__ pos_ptr, __half *__restrict__ k_cache, __half *__restrict__ v_cache,
                       __half *__restrict__ out, int heads, int max_len, float scale)
 {
     constexpr int HD = 32 * VPL;
-    __shared__ float q_s[HD], k_s[HD], v_s[HD];
+    constexpr int U = VPL >= 8 ? 2 : 4;   // cache rows in flight per warp
+    using Vec = typename HalfVec<VPL>::type;
+    __shared__ __align__(16) float q_s[HD], k_s[HD], v_s[HD];
     __shared__ float m_s[kAttnWarps], l_s[kAttnWarps];
-    __shared__ float acc_s[kAttnWarps][HD];
+    __shared__ __align__(16) float acc_s[kAttnWarps][HD];
+    __shared__ float part_acc[HD], part_ml[2];   // this CTA's merged partial result, read by the cluster's first CTA
     pdl_prologue();
-    const int head = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    long long pos64 = *pos_ptr;
+    unsigned crank, csize;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
+    const int head = blockIdx.x / csize, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long pos64 = *pos_ptr;
     const int pos = (int)(pos64 < 0 ? 0 : (pos64 >= max_len ? max_len - 1 : pos64));   // a position outside the cache is clamped
     if (warp == 0) {
-        const __half *q = qkv + (size_t)head * HD;
-        const __half *k = qkv + ((size_t)heads + head) * HD;
-        const __half *v = qkv + ((size_t)2 * heads + head) * HD;
-        float qf[VPL], kf[VPL];
+        const size_t at = (size_t)head * HD + VPL * lane;
+        float qf[VPL], kf[VPL], vf[VPL], cf[VPL], sf[VPL];
+        unpack_halfs<VPL>(__ldcg(reinterpret_cast<const Vec *>(qkv + at)), qf);
+        unpack_halfs<VPL>(__ldcg(reinterpret_cast<const Vec *>(qkv + (size_t)heads * HD + at)), kf);
+        const Vec vraw = __ldcg(reinterpret_cast<const Vec *>(qkv + (size_t)2 * heads * HD + at));
+        unpack_halfs<VPL>(vraw, vf);
+        unpack_halfs<VPL>(__ldg(reinterpret_cast<const Vec *>(cos_table + (size_t)pos * HD + VPL * lane)), cf);
+        unpack_halfs<VPL>(__ldg(reinterpret_cast<const Vec *>(sin_table + (size_t)pos * HD + VPL * lane)), sf);
+        float kr[VPL];
 #pragma unroll
         for (int j = 0; j < VPL; ++j) {
-            qf[j] = __half2float(__ldcg(q + j * 32 + lane));
-            kf[j] = __half2float(__ldcg(k + j * 32 + lane));
+            // rotate-half: the first half of the head pairs with -x[d + HD/2], the second with +x[d - HD/2]
+            const float qp = __shfl_xor_sync(0xffffffffu, qf[j], 16), kp = __shfl_xor_sync(0xffffffffu, kf[j], 16);
+            const float sign = lane < 16 ? -1.f : 1.f;
+            kr[j] = __half2float(__float2half_rn(kf[j] * cf[j] + sign * kp * sf[j]));
+            q_s[VPL * lane + j] = __half2float(__float2half_rn(qf[j] * cf[j] + sign * qp * sf[j])) * scale;
+            k_s[VPL * lane + j] = kr[j];
+            v_s[VPL * lane + j] = vf[j];
         }
-#pragma unroll
-        for (int j = 0; j < VPL; ++j) {
-            const int d = j * 32 + lane;
-            const float c = __half2float(__ldg(cos_table + (size_t)pos * HD + d));
-            const float s = __half2float(__ldg(sin_table + (size_t)pos * HD + d));
-            // rotate-half: first half pairs with -x[d + HD/2], second half with +x[d - HD/2]
-            const float qr = (j < VPL / 2) ? -qf[j + VPL / 2] : qf[j - VPL / 2];
-            const float kr = (j < VPL / 2) ? -kf[j + VPL / 2] : kf[j - VPL / 2];
-            const __half kh = __float2half_rn(kf[j] * c + kr * s);
-            const __half vh = __ldcg(v + d);
-            q_s[d] = __half2float(__float2half_rn(qf[j] * c + qr * s)) * scale;
-            k_s[d] = __half2float(kh);
-            v_s[d] = __half2float(vh);
-            k_cache[((size_t)head * max_len + pos) * HD + d] = kh;
-            v_cache[((size_t)head * max_len + pos) * HD + d] = vh;
+        if (crank == 0) {
+            const size_t row = ((size_t)head * max_len + pos) * HD + VPL * lane;
+            *reinterpret_cast<Vec *>(k_cache + row) = pack_halfs<VPL>(kr);
+            *reinterpret_cast<Vec *>(v_cache + row) = vraw;
         }
     }
     __syncthreads();
     float qf[VPL];
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) qf[j] = q_s[j * 32 + lane];
+    for (int j = 0; j < VPL; ++j) qf[j] = q_s[VPL * lane + j];
     float m = -INFINITY, l = 0.f, acc[VPL];
 #pragma unroll
     for (int j = 0; j < VPL; ++j) acc[j] = 0.f;
-    const __half *kc = k_cache + (size_t)head * max_len * HD;
-    const __half *vc = v_cache + (size_t)head * max_len * HD;
-#pragma unroll 2
-    for (int t = warp; t <= pos; t += kAttnWarps) {
-        float kf[VPL], vf[VPL];
-        if (t == pos) {
+    const __half *kc = k_cache + (size_t)head * max_len * HD + VPL * lane;
+    const __half *vc = v_cache + (size_t)head * max_len * HD + VPL * lane;
+    const int gw = (int)crank * kAttnWarps + warp, n_gw = (int)csize * kAttnWarps;
+    for (int t0 = gw; t0 <= pos; t0 += U * n_gw) {
+        Vec kraw[U], vraw[U];
 #pragma unroll
-            for (int j = 0; j < VPL; ++j) { kf[j] = k_s[j * 32 + lane]; vf[j] = v_s[j * 32 + lane]; }
-        } else {
-#pragma unroll
-            for (int j = 0; j < VPL; ++j) {
-                kf[j] = __half2float(__ldcg(kc + (size_t)t * HD + j * 32 + lane));
-                vf[j] = __half2float(__ldcg(vc + (size_t)t * HD + j * 32 + lane));
+        for (int u = 0; u < U; ++u) {
+            const int t = t0 + u * n_gw;
+            if (t < pos) {
+                kraw[u] = __ldcg(reinterpret_cast<const Vec *>(kc + (size_t)t * HD));
+                vraw[u] = __ldcg(reinterpret_cast<const Vec *>(vc + (size_t)t * HD));
             }
         }
-        float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < VPL; ++j) s += qf[j] * kf[j];
+        for (int u = 0; u < U; ++u) {
+            const int t = t0 + u * n_gw;
+            if (t > pos) break;   // warp-uniform
+            float kf[VPL], vf[VPL];
+            if (t == pos) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        const float m_new = fmaxf(m, s);
-        const float keep = __expf(m - m_new);   // 0 on the first row (m = -inf)
-        const float p = __expf(s - m_new);
-        l = l * keep + p;
+                for (int j = 0; j < VPL; ++j) { kf[j] = k_s[VPL * lane + j]; vf[j] = v_s[VPL * lane + j]; }
+            } else {
+                unpack_halfs<VPL>(kraw[u], kf);
+                unpack_halfs<VPL>(vraw[u], vf);
+            }
+            float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < VPL; ++j) acc[j] = acc[j] * keep + p * vf[j];
-        m = m_new;
+            for (int j = 0; j < VPL; ++j) s += qf[j] * kf[j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            const float m_new = fmaxf(m, s);
+            const float keep = __expf(m - m_new);   // 0 on a warp's first row (m = -inf)
+            const float p = __expf(s - m_new);
+            l = l * keep + p;
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) acc[j] = acc[j] * keep + p * vf[j];
+            m = m_new;
+        }
     }
     if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) acc_s[warp][j * 32 + lane] = acc[j];
+    for (int j = 0; j < VPL; ++j) acc_s[warp][VPL * lane + j] = acc[j];
     __syncthreads();
-    for (int d = threadIdx.x; d < HD; d += kAttnWarps * 32) {
-        float mm = -INFINITY;
+    // the CTA's partial result, not normalised: sum_w e^(m_w - M) acc_w, M, sum_w e^(m_w - M) l_w (a CTA
+    // without rows leaves M = -inf and zeros)
+    float mm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, m_s[w]);
+    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, m_s[w]);
+    for (int d = threadIdx.x; d < HD; d += kAttnWarps * 32) {
         float num = 0.f, den = 0.f;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) {
@@ -246,25 +313,47 @@ rope_attention_kernel(const __half *__restrict__ qkv, const __half *__restrict__
             num += f * acc_s[w][d];
             den += f * l_s[w];
         }
-        out[(size_t)head * HD + d] = __float2half_rn(num / den);
+        part_acc[d] = num;
+        if (d == 0) { part_ml[0] = mm; part_ml[1] = den; }
     }
+    if (csize > 1) cluster_barrier(); else __syncthreads();
+    if (crank == 0) {
+        for (int d = threadIdx.x; d < HD; d += kAttnWarps * 32) {
+            float big = -INFINITY;
+            for (unsigned r = 0; r < csize; ++r) big = fmaxf(big, csize > 1 ? ld_cluster_f32(&part_ml[0], r) : part_ml[0]);
+            float num = 0.f, den = 0.f;
+            for (unsigned r = 0; r < csize; ++r) {
+                const float mr = csize > 1 ? ld_cluster_f32(&part_ml[0], r) : part_ml[0];
+                const float f = (mr == -INFINITY) ? 0.f : __expf(mr - big);
+                num += f * (csize > 1 ? ld_cluster_f32(&part_acc[d], r) : part_acc[d]);
+                den += f * (csize > 1 ? ld_cluster_f32(&part_ml[1], r) : part_ml[1]);
+            }
+            out[(size_t)head * HD + d] = __float2half_rn(num / den);
+        }
+    }
+    if (csize > 1) cluster_barrier();   // the other CTAs' shared memory stays until the first one has read it
 }
 
 template <typename T> struct Same { using type = T; };
 
+// `cluster` > 1: thread-block clusters of that many CTAs along x (the grid is a multiple of it).
 template <typename... Args>
-int launch_pdl(const char *what, void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream,
+int launch_pdl(const char *what, void (*kernel)(Args...), dim3 grid, dim3 block, int cluster, cudaStream_t stream,
                typename Same<Args>::type... args)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = cluster > 1 ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
@@ -285,7 +374,7 @@ int macko_decode_add_rmsnorm(void *x, const void *pending, int n_pending, int64_
         (n_pending > 0 && pending_stride < n))
         return fail(MACKO_ERR_INVALID_ARGUMENT, "add_rmsnorm: n=%lld n_pending=%d stride=%lld or a null pointer",
                     (long long)n, n_pending, (long long)pending_stride);
-    return launch_pdl("add_rmsnorm", add_rmsnorm_kernel, dim3(1), dim3(kNormThreads), static_cast<cudaStream_t>(stream),
+    return launch_pdl("add_rmsnorm", add_rmsnorm_kernel, dim3(1), dim3(kNormThreads), 1, static_cast<cudaStream_t>(stream),
                       static_cast<__half *>(x), static_cast<const __half *>(pending), n_pending, (long long)pending_stride,
                       static_cast<const __half *>(weight), static_cast<__half *>(out), (int)n, eps);
 }
@@ -295,7 +384,7 @@ int macko_decode_silu_mul(const void *gate_up, void *out, int64_t n, void *strea
     if (!gate_up || !out || n <= 0 || n > (1 << 28))
         return fail(MACKO_ERR_INVALID_ARGUMENT, "silu_mul: n=%lld or a null pointer", (long long)n);
     const int ctas = (int)((n / 8 + 255) / 256) > 0 ? (int)((n / 8 + 255) / 256) : 1;
-    return launch_pdl("silu_mul", silu_mul_kernel, dim3(ctas > 296 ? 296 : ctas), dim3(256), static_cast<cudaStream_t>(stream),
+    return launch_pdl("silu_mul", silu_mul_kernel, dim3(ctas > 296 ? 296 : ctas), dim3(256), 1, static_cast<cudaStream_t>(stream),
                       static_cast<const __half *>(gate_up), static_cast<__half *>(out), (int)n);
 }
 
@@ -304,19 +393,28 @@ int macko_decode_rope_attention(const void *qkv, const void *cos_table, const vo
 {
     if (!qkv || !cos_table || !sin_table || !position || !k_cache || !v_cache || !out || heads <= 0 || max_len <= 0)
         return fail(MACKO_ERR_INVALID_ARGUMENT, "rope_attention: heads=%d max_len=%d or a null pointer", heads, max_len);
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256)
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "rope_attention: head_dim %d (64, 128 and 256 are built)", head_dim);
+    const void *ptrs[] = {qkv, cos_table, sin_table, k_cache, v_cache};
+    for (const void *p : ptrs)
+        if (!aligned(p, 16)) return fail(MACKO_ERR_MISALIGNED, "rope_attention: qkv, the tables and the caches must be 16-byte aligned");
     const float scale = 1.0f / sqrtf((float)head_dim);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const dim3 grid((unsigned)heads), block(kAttnWarps * 32);
+    // as many CTAs per head as keeps the grid within about one CTA per SM (clusters of up to 8 are portable)
+    const DeviceInfo *dev = nullptr;
+    if (int st = current_device_info(&dev)) return st;
+    int cluster = 8;
+    while (cluster > 1 && (long long)heads * cluster > dev->sm_count) cluster >>= 1;
+    const dim3 grid((unsigned)(heads * cluster)), block(kAttnWarps * 32);
 #define MACKO_ATTN(V)                                                                                                   \
-    return launch_pdl("rope_attention", rope_attention_kernel<V>, grid, block, s, static_cast<const __half *>(qkv),      \
+    return launch_pdl("rope_attention", rope_attention_kernel<V>, grid, block, cluster, s, static_cast<const __half *>(qkv), \
                       static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),                    \
                       reinterpret_cast<const long long *>(position), static_cast<__half *>(k_cache),                     \
                       static_cast<__half *>(v_cache), static_cast<__half *>(out), heads, max_len, scale)
     switch (head_dim) {
     case 64: MACKO_ATTN(2);
     case 128: MACKO_ATTN(4);
-    case 256: MACKO_ATTN(8);
-    default: return fail(MACKO_ERR_INVALID_ARGUMENT, "rope_attention: head_dim %d (64, 128 and 256 are built)", head_dim);
+    default: MACKO_ATTN(8);
     }
 #undef MACKO_ATTN
 }

@@ -165,13 +165,18 @@ class ColumnShardedMackoLinear(nn.Module):
         torch.cuda.synchronize(values.device)   # the compressor has finished: the block is final from here on
         self._c0_ptr = values.data_ptr()
 
-    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+    def partials(self, x_local: torch.Tensor) -> torch.Tensor:
+        """The N partial output vectors [N, out] (rank order), not yet added: a view of the exchange slot, to be
+        consumed (in stream order) before the second-next product through the same `PeerGather`."""
         if x_local.dim() != 1 or x_local.shape[0] != self.in_local:
             raise RuntimeError(f"expected this rank's {self.in_local} input features, got {tuple(x_local.shape)}")
         final = self.c_0.data_ptr() == self._c0_ptr
         parts = self.peer.multiply(self.shard, x_local.contiguous(), immutable=final)
+        return parts.view(self.peer.world, self.out_features)
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
         # one reduction kernel: torch adds fp16 inputs in fp32 and rounds once, in rank order on every rank
-        return parts.view(self.peer.world, self.out_features).sum(dim=0)
+        return self.partials(x_local).sum(dim=0)
 
 
 def compress_state_dict(state_dict, select=lambda name: ("self_attn" in name or "mlp" in name) and name.endswith(".weight")):

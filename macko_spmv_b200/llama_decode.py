@@ -18,6 +18,11 @@ the o and down projections that its slice of the attention output / MLP activati
 (`ColumnShardedMackoLinear`: partial products of all ranks are exchanged by the SpMV kernel itself and added).
 A token therefore costs two fused product+exchange kernels per block plus one for the row-sharded LM head
 (`RowShardedMackoLinear`), and no collective call; norms and rotary embedding are replicated.
+
+The decode step runs the code between the products as three kernels of this package per block
+(`torch.ops.macko_spmv.add_rmsnorm`, `rope_attention`, `silu_mul`: residual add + RMSNorm, rotary embedding +
+KV-cache append + attention, SwiGLU gate), eight launches per block in all, for MACKO and dense layers alike;
+`LlamaDecoder(..., fused_glue=False)` and `Block.forward` keep the same step in plain PyTorch operators.
 """
 from __future__ import annotations
 
@@ -132,6 +137,17 @@ class Block(nn.Module):
         return x + self.down_proj(torch.nn.functional.silu(gu[: self.ffn]) * gu[self.ffn :])
 
 
+    def step_fused(self, x, pending, pos, cos_table, sin_table):
+        """The same block as `forward` with three kernels of this package between the four products. `x` [hidden]
+        is the residual stream, updated in place; `pending` [k, hidden] holds output vectors that have not been
+        added to it yet (the previous block's down projection: one vector, or one partial vector per rank).
+        Returns this block's own pending output."""
+        ops = torch.ops.macko_spmv
+        qkv = self.qkv_proj(ops.add_rmsnorm(x, pending, self.input_norm.weight, self.input_norm.eps))
+        attn = ops.rope_attention(qkv, cos_table, sin_table, pos, self.k_cache, self.v_cache)
+        gu = self.gate_up_proj(ops.add_rmsnorm(x, _pending_output(self.o_proj, attn), self.post_norm.weight, self.post_norm.eps))
+        return _pending_output(self.down_proj, ops.silu_mul(gu))
+
     def prefill(self, x, cos, sin):
         """All prompt positions at once: x [T, hidden], cos/sin [T, head_dim]. Fills cache rows 0..T-1."""
         T = x.shape[0]
@@ -148,6 +164,14 @@ class Block(nn.Module):
         return x + self.down_proj(torch.nn.functional.silu(gu[:, : self.ffn]) * gu[:, self.ffn :])
 
 
+def _pending_output(layer, x):
+    """The output of a projection as rows still to be added to the residual stream: [1, out], or the [N, out]
+    partial vectors of a column-sharded layer (left in the exchange buffer: the next kernel adds them up)."""
+    if isinstance(layer, ColumnShardedMackoLinear):
+        return layer.partials(x)
+    return layer(x).view(1, -1)
+
+
 def _rope(t, cos, sin):
     # rotate-half convention: (t1, t2) -> (t1*cos - t2*sin, t2*cos + t1*sin), cos/sin repeated over both halves
     half = t.shape[-1] // 2
@@ -157,8 +181,9 @@ def _rope(t, cos, sin):
 
 class LlamaDecoder(nn.Module):
     def __init__(self, density: float, cfg=None, layers=None, device="cuda", max_len=384, seed=4000,
-                 prune_lm_head=True, peer=None):
+                 prune_lm_head=True, peer=None, fused_glue=True):
         super().__init__()
+        self.fused_glue = fused_glue
         cfg = dict(LLAMA2_7B if cfg is None else cfg)
         if layers is not None:
             cfg["layers"] = layers
@@ -199,6 +224,11 @@ class LlamaDecoder(nn.Module):
     def logits(self, token, pos):
         """fp16 logits [vocab] of the token at position `pos`; updates the KV cache."""
         x = self.embed.index_select(0, token)[0]
+        if self.fused_glue:
+            pending = x.new_empty((0, x.shape[0]))
+            for blk in self.blocks:
+                pending = blk.step_fused(x, pending, pos, self.cos_table, self.sin_table)
+            return self.lm_head(torch.ops.macko_spmv.add_rmsnorm(x, pending, self.norm.weight, self.norm.eps))
         cos = self.cos_table.index_select(0, pos)[0]
         sin = self.sin_table.index_select(0, pos)[0]
         mask = torch.where(self.positions <= pos, self.zero, self.neg_inf).view(1, 1, 1, -1)

@@ -158,6 +158,14 @@ def test_new_entry_points_validate_before_touching_the_device():
     assert lib.macko_spmv_fp16_scatter_ex(a16, a16, a16, 4, 8, 8, a16, ptrs, 0, ptrs, 2, 2, 0, 0, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_peer_wait_limited(None, 2, 10, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_compress_overflow(None, None) == cabi.ERR_INVALID_ARGUMENT
+    # decode helpers: sizes, null pointers, head sizes that are not built
+    assert lib.macko_decode_add_rmsnorm(a16, None, 1, 64, a16, a16, 64, 1e-5, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_decode_add_rmsnorm(a16, a16, 2, 32, a16, a16, 64, 1e-5, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_decode_add_rmsnorm(a16, None, 0, 0, a16, a16, 0, 1e-5, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_decode_silu_mul(a16, None, 64, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_decode_rope_attention(a16, a16, a16, a16, a16, a16, a16, 4, 96, 16, None) == cabi.ERR_INVALID_ARGUMENT
+    assert b"head_dim" in lib.macko_last_error()
+    assert lib.macko_decode_rope_attention(a16, a16, a16, None, a16, a16, a16, 4, 128, 16, None) == cabi.ERR_INVALID_ARGUMENT
 
 
 def test_plan_model_of_the_oracle_on_the_reference_vector(reference_vectors):
