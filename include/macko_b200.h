@@ -365,7 +365,8 @@ int macko_peer_forward(void *const *peer_y, int64_t row_offset, int64_t rows, ui
  *
  * macko_decode_add_rmsnorm: x[i] += pending[0][i] + ... + pending[n_pending-1][i] (row p of `pending` starts at
  *   pending + p * pending_stride elements; fp32 sum in that order, rounded once; n_pending may be 0), then
- *   out[i] = x[i] * rsqrt(mean(x^2) + eps) * weight[i]. x is updated in place; out must not alias x.
+ *   out[i] = x[i] * rsqrt(mean(x^2) + eps) * weight[i]. x is updated in place; out must not alias x. `weight`
+ *   is read ahead of stream order (a parameter: it must not be written by work still in flight on `stream`).
  * macko_decode_rope_attention: qkv = [3][heads][head_dim] (q, k, v of the new token); rotary embedding
  *   (rotate-half convention, tables [max_len][head_dim] with both halves equal) of q and k at *position
  *   (an int64 on the device, clamped into [0, max_len)), k and v stored into row *position of the caches

@@ -44,19 +44,26 @@ __device__ __forceinline__ float block_sum(float v, float *scratch)
 
 // One CTA. x (fp16, n elements) is the residual stream: x[i] <- x[i] + pending[0][i] + pending[1][i] + ...
 // (fp32 sum in that order, rounded to fp16 once), then out[i] = x[i] * rsqrt(mean(x^2) + eps) * weight[i]
-// with the rounded x, all in fp32, rounded to fp16. n_pending may be 0.
+// with the rounded x, all in fp32, rounded to fp16. n_pending may be 0. The weight (a parameter, not the output
+// of the kernel in front) is fetched before the wait for that kernel; a thread keeps its first eight elements
+// in registers between the two passes (all of them when n <= 4096).
 __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ pending, int n_pending, long long pending_stride,
                    const __half *__restrict__ weight, __half *__restrict__ out, int n, float eps)
 {
     __shared__ float scratch[32];
-    pdl_prologue();
-    float sq = 0.f;
     const bool vec = (n & 7) == 0 && (pending_stride & 7) == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(pending) |
                        reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int n_vec = vec ? n >> 3 : 0;
+    asm volatile("griddepcontrol.launch_dependents;");
+    uint4 w_first = make_uint4(0u, 0u, 0u, 0u);
+    if ((int)threadIdx.x < n_vec) w_first = __ldg(reinterpret_cast<const uint4 *>(weight) + threadIdx.x);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float sq = 0.f;
+    uint4 x_first = make_uint4(0u, 0u, 0u, 0u);
     if (vec) {
-        for (int c = threadIdx.x; c < (n >> 3); c += kNormThreads) {
+        for (int c = threadIdx.x; c < n_vec; c += kNormThreads) {
             uint4 xv = reinterpret_cast<const uint4 *>(x)[c];
             __half2 *xh = reinterpret_cast<__half2 *>(&xv);
             float f[8];
@@ -83,6 +90,7 @@ add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ pending, i
                 sq += t.x * t.x + t.y * t.y;
             }
             if (n_pending > 0) reinterpret_cast<uint4 *>(x)[c] = xv;
+            if (c == (int)threadIdx.x) x_first = xv;
         }
     } else {
         for (int i = threadIdx.x; i < n; i += kNormThreads) {
@@ -96,11 +104,12 @@ add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ pending, i
     }
     const float total = block_sum(sq, scratch);
     const float rstd = rsqrtf(total / (float)n + eps);
-    // second pass: every thread re-reads the elements it wrote itself
+    // second pass: every thread handles the elements it wrote itself
     if (vec) {
-        for (int c = threadIdx.x; c < (n >> 3); c += kNormThreads) {
-            const uint4 xv = reinterpret_cast<const uint4 *>(x)[c];
-            const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(weight) + c);
+        for (int c = threadIdx.x; c < n_vec; c += kNormThreads) {
+            const bool first = c == (int)threadIdx.x;
+            const uint4 xv = first ? x_first : reinterpret_cast<const uint4 *>(x)[c];
+            const uint4 wv = first ? w_first : __ldg(reinterpret_cast<const uint4 *>(weight) + c);
             const __half2 *xh = reinterpret_cast<const __half2 *>(&xv);
             const __half2 *wh = reinterpret_cast<const __half2 *>(&wv);
             uint4 ov;
