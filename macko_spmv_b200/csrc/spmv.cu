@@ -259,6 +259,20 @@ struct NoPlan {};
 template <bool P> using PeersArg = std::conditional_t<P, Peers, NoPeers>;
 template <bool P> using PlanArg = std::conditional_t<P, PlanView, NoPlan>;
 
+// First row of warp `w` of `n_warps` when the rows are dealt to the warps in blocks of K as evenly as they go:
+// K * floor(n_blocks * w / n_warps), capped at rows. A 32-bit division whenever the product fits (every matrix of
+// fewer than 2^32 / n_warps row blocks: a 64-bit division is some hundred instructions, in every warp of the grid).
+template <int K>
+__device__ __forceinline__ int block_boundary(int rows, unsigned w, unsigned n_warps)
+{
+    const unsigned n_blocks = ((unsigned)rows + K - 1) / K;
+    unsigned b;
+    if (__umulhi(n_blocks, n_warps) == 0u) b = n_blocks * w / n_warps;   // w <= n_warps: the product fits 32 bits
+    else b = (unsigned)((unsigned long long)n_blocks * w / n_warps);
+    const unsigned long long r = (unsigned long long)b * K;
+    return (int)(r < (unsigned long long)rows ? r : (unsigned long long)rows);
+}
+
 // What a launch carries besides the reference's arguments.
 struct Extra {
     unsigned flags;               // MACKO_SPMV_MATRIX_IMMUTABLE
@@ -332,9 +346,8 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
             if (last_blk == nb - 1) row_hi -= nb * K - V;   // the very last block may hold fewer than K
         }
     } else {
-        const long long n_blocks = ((long long)rows + K - 1) / K;
-        row_next = (int)min((long long)rows, (n_blocks * warp_id / n_warps) * K);
-        row_hi = (int)min((long long)rows, (n_blocks * (warp_id + 1) / n_warps) * K);
+        row_next = block_boundary<K>(rows, (unsigned)warp_id, (unsigned)n_warps);
+        row_hi = block_boundary<K>(rows, (unsigned)warp_id + 1u, (unsigned)n_warps);
     }
     // sorted index of position p of this warp's sequence (planned)
     auto sorted_index = [&](int p) -> int {
@@ -346,10 +359,9 @@ spmv_kernel(const uint4 *__restrict__ values, const unsigned *__restrict__ delta
     // PEER: rows of the whole CTA (its warps own consecutive ranges) and the staging area for their y
     int cta_row_lo = 0, cta_row_hi = 0;
     if constexpr (PEER) {
-        const long long n_blocks = ((long long)rows + K - 1) / K;
-        const long long cta_w0 = (long long)blockIdx.x * kWarpsPerCta;
-        cta_row_lo = (int)min((long long)rows, (n_blocks * cta_w0 / n_warps) * K);
-        cta_row_hi = (int)min((long long)rows, (n_blocks * (cta_w0 + kWarpsPerCta) / n_warps) * K);
+        const unsigned cta_w0 = blockIdx.x * kWarpsPerCta;
+        cta_row_lo = block_boundary<K>(rows, cta_w0, (unsigned)n_warps);
+        cta_row_hi = block_boundary<K>(rows, cta_w0 + kWarpsPerCta, (unsigned)n_warps);
     }
     __half *ystage = reinterpret_cast<__half *>(smem + (((size_t)(kXPadFront + cols + kXPadBack) * sizeof(__half) + 15) & ~(size_t)15));
 
