@@ -374,12 +374,15 @@ int macko_peer_forward(void *const *peer_y, int64_t row_offset, int64_t rows, ui
  *   0..*position. One CTA per head: built for the contexts of a benchmark (hundreds of positions), not for
  *   long ones. head_dim 64, 128 or 256.
  * macko_decode_silu_mul: out[i] = silu(gate_up[i]) * gate_up[n + i], i < n.
+ * macko_decode_argmax: *index (an int64 on the device) = position of the largest of n fp16 values, the lowest
+ *   position among equal ones; NaN never wins (greedy choice of the next token from the logits).
  */
 int macko_decode_add_rmsnorm(void *x, const void *pending, int n_pending, int64_t pending_stride, const void *weight,
                              void *out, int64_t n, float eps, void *stream);
 int macko_decode_rope_attention(const void *qkv, const void *cos_table, const void *sin_table, const int64_t *position,
                                 void *k_cache, void *v_cache, void *out, int heads, int head_dim, int max_len, void *stream);
 int macko_decode_silu_mul(const void *gate_up, void *out, int64_t n, void *stream);
+int macko_decode_argmax(const void *values, int64_t n, int64_t *index, void *stream);
 
 #ifdef __cplusplus
 }

@@ -111,6 +111,11 @@ def _silu_mul_fake(gate_up):
     return gate_up.new_empty((gate_up.shape[0] // 2,))
 
 
+@torch.library.register_fake("macko_spmv::argmax")
+def _argmax_fake(values):
+    return values.new_empty((1,), dtype=torch.int64)
+
+
 def move_to_device(compressed, device):
     """Move the three buffers of a compressed matrix (src/macko_spmv/__init__.py:110-117)."""
     return (

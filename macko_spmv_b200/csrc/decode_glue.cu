@@ -1,11 +1,12 @@
 // The element-wise and attention steps between the matrix-vector products of a batch-1 decode step of a
-// Llama-architecture transformer, as three kernels per block instead of some twenty library kernels:
+// Llama-architecture transformer, as three kernels per block instead of some twenty library kernels (plus one per token):
 //
 //   add_rmsnorm      x += sum of the pending output vectors (the previous product's y, or the N partial y of a
 //                    column-sharded layer), then out = rmsnorm(x) * weight
 //   rope_attention   rotary embedding of q and k at position pos, k and v appended to the cache, softmax
 //                    attention of q over cache rows 0..pos (one CTA per head)
 //   silu_mul         out = silu(gate) * up
+//   argmax           the greedy choice of the next token from the fp16 logits
 //
 // The reference measures tokens/s of a Hugging Face model whose projections are swapped for MACKO layers
 // (python_scripts/util_run_pruned_llm.py:102-133, 159-207); the model code around the projections is the
@@ -154,6 +155,50 @@ silu_mul_kernel(const __half *__restrict__ gu, __half *__restrict__ out, int n)
             const float g = __half2float(__ldcg(gu + i)), u = __half2float(__ldcg(gu + n + i));
             out[i] = __float2half_rn(g / (1.f + __expf(-g)) * u);
         }
+    }
+}
+
+// Index of the largest of n fp16 values (the lowest index among equal ones; NaN never wins), as one int64: the
+// greedy choice of the next token. One CTA.
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const __half *__restrict__ v, int n, long long *__restrict__ out)
+{
+    __shared__ float best_s[32];
+    __shared__ int idx_s[32];
+    pdl_prologue();
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0) {
+        for (int c = threadIdx.x; c < (n >> 3); c += 1024) {
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(v) + c);
+            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 t = __half22float2(h[j]);
+                if (t.x > best) { best = t.x; idx = 8 * c + 2 * j; }
+                if (t.y > best) { best = t.y; idx = 8 * c + 2 * j + 1; }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += 1024) {
+            const float t = __half2float(__ldcg(v + i));
+            if (t > best) { best = t; idx = i; }
+        }
+    }
+    auto merge = [&](float ob, int oi) {
+        if (ob > best || (ob == best && oi < idx)) { best = ob; idx = oi; }
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) merge(__shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { best_s[warp] = best; idx_s[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        best = best_s[lane];
+        idx = idx_s[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) merge(__shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+        if (lane == 0) *out = idx == 0x7fffffff ? 0 : idx;   // all -inf or NaN: index 0
     }
 }
 
@@ -395,6 +440,14 @@ int macko_decode_silu_mul(const void *gate_up, void *out, int64_t n, void *strea
     const int ctas = (int)((n / 8 + 255) / 256) > 0 ? (int)((n / 8 + 255) / 256) : 1;
     return launch_pdl("silu_mul", silu_mul_kernel, dim3(ctas > 296 ? 296 : ctas), dim3(256), 1, static_cast<cudaStream_t>(stream),
                       static_cast<const __half *>(gate_up), static_cast<__half *>(out), (int)n);
+}
+
+int macko_decode_argmax(const void *values, int64_t n, int64_t *index, void *stream)
+{
+    if (!values || !index || n <= 0 || n > (1 << 30))
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "argmax: n=%lld or a null pointer", (long long)n);
+    return launch_pdl("argmax", argmax_kernel, dim3(1), dim3(1024), 1, static_cast<cudaStream_t>(stream),
+                      static_cast<const __half *>(values), (int)n, reinterpret_cast<long long *>(index));
 }
 
 int macko_decode_rope_attention(const void *qkv, const void *cos_table, const void *sin_table, const int64_t *position,

@@ -325,6 +325,17 @@ at::Tensor silu_mul_cuda(const at::Tensor &gate_up)
     return out;
 }
 
+at::Tensor argmax_cuda(const at::Tensor &values)
+{
+    check_half_vec(values, "values");
+    TORCH_CHECK(values.dim() == 1 && values.size(0) > 0, "values must be a non-empty vector");
+    const c10::cuda::CUDAGuard guard(values.device());
+    at::Tensor out = at::empty({1}, values.options().dtype(at::kLong));
+    check_status(macko_decode_argmax(values.data_ptr(), values.size(0), out.data_ptr<int64_t>(), c10::cuda::getCurrentCUDAStream()),
+                 "macko_decode_argmax");
+    return out;
+}
+
 }  // namespace
 
 TORCH_LIBRARY(macko_spmv, m)
@@ -345,6 +356,7 @@ TORCH_LIBRARY(macko_spmv, m)
     m.def("rope_attention(Tensor qkv, Tensor cos_table, Tensor sin_table, Tensor position, Tensor(a!) k_cache, "
           "Tensor(b!) v_cache) -> Tensor");
     m.def("silu_mul(Tensor gate_up) -> Tensor");
+    m.def("argmax(Tensor values) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
@@ -361,4 +373,5 @@ TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
     m.impl("add_rmsnorm", &add_rmsnorm_cuda);
     m.impl("rope_attention", &rope_attention_cuda);
     m.impl("silu_mul", &silu_mul_cuda);
+    m.impl("argmax", &argmax_cuda);
 }

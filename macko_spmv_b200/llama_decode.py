@@ -208,6 +208,8 @@ class LlamaDecoder(nn.Module):
 
     def step(self, token, pos):
         """token int64[1], pos int64[1] (device tensors) -> next token int64[1] (greedy)."""
+        if self.fused_glue:
+            return torch.ops.macko_spmv.argmax(self.logits(token, pos))
         return torch.argmax(self.logits(token, pos).float(), dim=-1, keepdim=True)
 
     def prefill(self, tokens):

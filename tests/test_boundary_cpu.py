@@ -163,6 +163,7 @@ def test_new_entry_points_validate_before_touching_the_device():
     assert lib.macko_decode_add_rmsnorm(a16, a16, 2, 32, a16, a16, 64, 1e-5, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_decode_add_rmsnorm(a16, None, 0, 0, a16, a16, 0, 1e-5, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_decode_silu_mul(a16, None, 64, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_decode_argmax(a16, 0, a16, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_decode_rope_attention(a16, a16, a16, a16, a16, a16, a16, 4, 96, 16, None) == cabi.ERR_INVALID_ARGUMENT
     assert b"head_dim" in lib.macko_last_error()
     assert lib.macko_decode_rope_attention(a16, a16, a16, None, a16, a16, a16, 4, 128, 16, None) == cabi.ERR_INVALID_ARGUMENT

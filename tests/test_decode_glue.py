@@ -117,3 +117,16 @@ def test_fused_decode_step_matches_the_pytorch_step():
             for blk_a, blk_b in zip(a.blocks, b.blocks):
                 ka, kb = blk_a.k_cache[:, :, :10].float(), blk_b.k_cache[:, :, :10].float()
                 assert float((ka - kb).norm() / kb.norm()) < 1e-2
+
+
+@pytest.mark.parametrize("n", [32000, 1000, 37, 8, 1])
+def test_argmax(n):
+    v = torch.randn(n, device="cuda", generator=_gen(n)).half()
+    assert int(ops.argmax(v)) == int(torch.argmax(v.float()))
+    v[n // 2] = 100.0
+    v[n - 1] = 100.0                          # equal maxima: the lowest index wins
+    assert int(ops.argmax(v)) == n // 2
+    v[0] = float("nan")                       # NaN never wins
+    assert int(ops.argmax(v)) == (n // 2 if n > 1 else 0)
+    v.fill_(float("-inf"))
+    assert int(ops.argmax(v)) == 0
