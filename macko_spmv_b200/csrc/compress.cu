@@ -9,8 +9,9 @@
 // as zero (cpu_compressor.cuh:26-27,36).
 //
 // Phase 1 (count):  one warp per row -> stored elements per row -> prefix sum = row_indices.
-// Phase 2 (emit):   one warp per row -> values and one delta per byte into scratch;
-//                   a final pass packs two deltas per byte and zeroes the tail up to P.
+// Phase 2 (emit):   one warp per row -> values and packed deltas in one pass (emit_rows_packed_kernel);
+//                   the built-in-scratch entry point and the int8 encoder write one delta per byte into
+//                   scratch and a final pass packs two per byte and zeroes the tail up to P.
 // A warp reads 256 columns per step (one 128-bit load per lane, aligned on the matrix
 // allocation, not on the row, so odd column counts still use vector loads).
 #include "common.cuh"
@@ -206,6 +207,193 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
     } else {
         if (__any_sync(0xffffffffu, refused) && lane == 0) atomicAdd(&g_compress_overflow, 1u);
     }
+}
+
+// ---- emit with packed deltas ---------------------------------------------------------------------------
+// The emit phase of macko_compress_emit / _emit_bf16: values and the packed 4-bit deltas in one pass, no scratch
+// and no packing pass. A warp walks its row as above and appends what a step stores to a small ring in shared
+// memory whose slot j stands for output slot ring_base + j, ring_base a multiple of 8. Whenever the ring could
+// not take another step, all complete groups of 8 slots leave: the values as one 16-byte store, their 8 deltas packed into one 32-bit
+// store. The first and the last group of a row may be shared with the neighbouring rows (rows start at
+// arbitrary slots): their values leave one by one and their nibbles are merged into the word with atomicOr,
+// which is why the caller clears `deltas` before the launch. Pads: only a lane's first non-zero of a step can
+// have pads in front of it (later ones are less than 8 columns apart). The run in front of the first non-zero
+// of the whole step can be as long as the row and is written by the warp together, 256 pads at a time; the
+// others (at most 15 per lane, 16 per step) by their lane. The warp of the last row also clears values[n, P).
+constexpr int kRing = 544;   // room for two appends: what stays after a flush (< 8), then twice 256 non-zeros + 16 pads
+constexpr int kRingFlushAbove = kRing - 272;   // a step (or a batch of 256 pads) always fits below kRing
+
+// The 8 deltas of bytes b0..b7 (each < 16) as 8 nibbles, the first in the low nibble.
+__device__ __forceinline__ unsigned pack_nibbles(uint2 b)
+{
+    b.x &= 0x0f0f0f0fu;   // ring entries of another row hold anything
+    b.y &= 0x0f0f0f0fu;
+    unsigned x = (b.x | (b.x >> 4)) & 0x00ff00ffu;
+    x = (x | (x >> 8)) & 0xffffu;
+    unsigned y = (b.y | (b.y >> 4)) & 0x00ff00ffu;
+    y = (y | (y >> 8)) & 0xffffu;
+    return x | (y << 16);
+}
+
+template <typename V>
+struct EmitRing {
+    V *sv;                  // values of the ring's slots
+    unsigned char *sn;      // their deltas, one per byte
+    int base;               // output slot of ring slot 0 (a multiple of 8)
+    int fill;               // ring slots in use (warp-uniform)
+    int own_lo;             // first output slot that belongs to this row
+    bool refused;
+};
+
+// Writes out the complete groups of 8 ring slots (`last`: the incomplete one as well), keeps the rest.
+template <typename V>
+__device__ __forceinline__ void ring_flush(EmitRing<V> &r, V *__restrict__ values, unsigned *__restrict__ deltas32,
+                                           int limit, bool vec_v, bool last, int lane)
+{
+    __syncwarp();
+    const int n_full = r.fill >> 3;
+    const int n_groups = n_full + ((last && (r.fill & 7)) ? 1 : 0);
+    for (int c = lane; c < n_groups; c += 32) {
+        const int slot0 = r.base + 8 * c;
+        const int lo = max(r.own_lo - slot0, 0);                 // first ring entry of the group that is this row's
+        const int hi = c < n_full ? 8 : (r.fill & 7);            // one past its last
+        if (lo >= hi) continue;
+        const uint2 nb = *reinterpret_cast<const uint2 *>(r.sn + 8 * c);
+        unsigned packed = pack_nibbles(nb);
+        if (lo == 0 && hi == 8 && slot0 + 8 <= limit) {
+            if (vec_v && sizeof(V) == 2) {
+                *reinterpret_cast<uint4 *>(values + slot0) = *reinterpret_cast<const uint4 *>(r.sv + 8 * c);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) values[slot0 + j] = r.sv[8 * c + j];
+            }
+            deltas32[slot0 >> 3] = packed;
+        } else {
+            unsigned mask = 0xffffffffu << (4 * lo);
+            if (hi < 8) mask &= ~(0xffffffffu << (4 * hi));
+            for (int j = lo; j < hi; ++j) {
+                if (slot0 + j < limit) {
+                    values[slot0 + j] = r.sv[8 * c + j];
+                } else {
+                    mask &= ~(0xfu << (4 * j));
+                    r.refused = true;
+                }
+            }
+            if ((packed & mask) != 0u && slot0 < limit) atomicOr(deltas32 + (slot0 >> 3), packed & mask);
+        }
+    }
+    __syncwarp();
+    // the incomplete group moves to the front
+    const int rest = r.fill & 7;
+    V keep_v = 0;
+    unsigned char keep_n = 0;
+    if (lane < rest) { keep_v = r.sv[8 * n_full + lane]; keep_n = r.sn[8 * n_full + lane]; }
+    __syncwarp();
+    if (lane < rest) { r.sv[lane] = keep_v; r.sn[lane] = keep_n; }
+    r.base += 8 * n_full;
+    r.fill = rest;
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(kThreads)
+emit_rows_packed_kernel(const unsigned short *__restrict__ dense, int rows, int cols, bool vec_ok,
+                        const int *__restrict__ row_indices, unsigned short *__restrict__ values,
+                        unsigned *__restrict__ deltas32, int limit, unsigned nan_above, bool vec_v)
+{
+    __shared__ __align__(16) unsigned short ring_v[kWarpsPerCta][kRing];
+    __shared__ __align__(8) unsigned char ring_n[kWarpsPerCta][kRing];
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const long long total = (long long)rows * cols;
+    const long long row_lo = (long long)row * cols;
+    const long long row_hi = row_lo + cols;
+    const long long first = vec_ok ? (row_lo & ~7LL) : row_lo;
+
+    EmitRing<unsigned short> ring;
+    ring.sv = ring_v[threadIdx.x >> 5];
+    ring.sn = ring_n[threadIdx.x >> 5];
+    const int out0 = min(max(row_indices[row], 0), limit);   // a corrupt offset cannot leave the buffers
+    ring.base = out0 & ~7;
+    ring.fill = out0 & 7;
+    ring.own_lo = out0;
+    ring.refused = row_indices[row] != out0;
+    int carry_prev = -1;   // column of the last non-zero seen so far in this row
+
+    for (long long group0 = first; group0 < row_hi; group0 += (long long)kUnroll * kColsPerStep) {
+        unsigned ws[kUnroll][4];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            load8(dense, group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane, total, vec_ok, ws[u]);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const long long g0 = group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane;
+            const unsigned (&w)[4] = ws[u];
+            const int c0 = (int)(g0 - row_lo);  // column of element 0; may be negative on the first step
+            unsigned nz = nonzero_bits(w);
+            if (g0 < row_lo || g0 + 8 > row_hi) nz &= row_bits(g0, row_lo, row_hi);
+            const unsigned any = __ballot_sync(0xffffffffu, nz != 0);
+            if (any == 0) continue;  // warp-uniform
+            const int my_last = c0 + (31 - __clz(nz | 1u));
+            const int prev = prev_nonzero_before_lane(any, lane, my_last, carry_prev);
+            const int c_first = c0 + __ffs(nz) - 1;   // meaningless when nz == 0
+            int npad = nz ? (c_first - prev - 1) >> 4 : 0;
+
+            // the pads in front of the step's first non-zero: the zeros behind carry_prev, by the whole warp
+            const int leader = __ffs(any) - 1;
+            const int lead_pads = __shfl_sync(0xffffffffu, npad, leader);
+            if (lane == leader) npad = 0;
+            for (int b0 = 0; b0 < lead_pads; b0 += 256) {
+                const int n = min(256, lead_pads - b0);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int i = lane + 32 * q;
+                    if (i < n) {
+                        ring.sv[ring.fill + i] = __ldg(dense + row_lo + carry_prev + 16 * (b0 + i + 1));   // the +-0 it sits on
+                        ring.sn[ring.fill + i] = 15;
+                    }
+                }
+                ring.fill += n;
+                if (ring.fill > kRingFlushAbove) ring_flush(ring, values, deltas32, limit, vec_v, false, lane);
+            }
+            carry_prev = __shfl_sync(0xffffffffu, my_last, 31 - __clz(any));
+
+            const int mine = npad + __popc(nz);
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const int step_total = __shfl_sync(0xffffffffu, incl, 31);
+            int k = ring.fill + incl - mine;
+            for (int q = 1; q <= npad; ++q) {           // rare: a gap of 16 or more zeros inside the step
+                ring.sv[k] = __ldg(dense + row_lo + prev + 16 * q);
+                ring.sn[k] = 15;
+                ++k;
+            }
+            int before = prev;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (nz & (1u << i)) {
+                    ring.sv[k] = canonical((unsigned short)((w[i >> 1] >> (16 * (i & 1))) & 0xffffu), nan_above);
+                    ring.sn[k] = (unsigned char)((c0 + i - before - 1) & 15);
+                    ++k;
+                    before = c0 + i;
+                }
+            }
+            ring.fill += step_total;
+            if (ring.fill > kRingFlushAbove) ring_flush(ring, values, deltas32, limit, vec_v, false, lane);
+        }
+    }
+    ring_flush(ring, values, deltas32, limit, vec_v, true, lane);
+    if (row == rows - 1) {
+        // everything from n = row_indices[rows] to the padded count is zero (the deltas already are)
+        const int n = row_indices[rows];
+        if (n < 0 || n > limit) ring.refused = true;   // row_indices and P do not belong together
+        for (int i = max(n, 0) + lane; i < limit; i += 32) values[i] = 0;
+    }
+    if (__any_sync(0xffffffffu, ring.refused) && lane == 0) atomicAdd(&g_compress_overflow, 1u);
 }
 
 // In-place inclusive prefix sum over counts[1..rows]; counts[0] = 0. One CTA, four rows per thread
@@ -490,20 +678,21 @@ static int compress_emit_typed(const void *dense, int64_t rows, int64_t cols, co
         return fail(MACKO_ERR_WORKSPACE, "workspace has %lld bytes, %lld needed", (long long)workspace_bytes,
                     (long long)macko_compress_workspace_bytes(padded_count));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Boundary groups of neighbouring rows merge their nibbles into one word: the deltas start at zero. The
+    // workspace is not used any more by this entry point (its size is still checked: callers size it once).
+    cudaError_t e = cudaMemsetAsync(deltas, 0, (size_t)padded_count / 2, s);
+    if (e == cudaSuccess && rows == 0) e = cudaMemsetAsync(values, 0, (size_t)padded_count * 2, s);
+    if (e != cudaSuccess) return fail(MACKO_ERR_CUDA, "clearing the outputs: %s", cudaGetErrorString(e));
     if (rows > 0) {
         const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
-        compress_rows_kernel<true><<<grid, kThreads, 0, s>>>(
-            static_cast<const unsigned short *>(dense), (int)rows, (int)cols, aligned(dense, 16),
-            nullptr, row_indices, static_cast<unsigned short *>(values), static_cast<unsigned char *>(workspace),
-            (int)padded_count, nan_above);
+        emit_rows_packed_kernel<<<grid, kThreads, 0, s>>>(
+            static_cast<const unsigned short *>(dense), (int)rows, (int)cols, aligned(dense, 16), row_indices,
+            static_cast<unsigned short *>(values), static_cast<unsigned *>(deltas), (int)padded_count, nan_above,
+            aligned(values, 16));
         st = launch_error("compress emit launch");
         if (st != MACKO_OK) return st;
     }
-    const int groups = (int)(padded_count / 8);
-    pack_kernel<unsigned short><<<(groups + 255) / 256, 256, 0, s>>>(
-        static_cast<const uint2 *>(workspace), row_indices, (int)rows, groups,
-        static_cast<unsigned *>(deltas), static_cast<unsigned short *>(values));
-    return launch_error("pack launch");
+    return MACKO_OK;
 }
 
 int macko_compress_emit(const void *dense, int64_t rows, int64_t cols, const int32_t *row_indices,

@@ -106,8 +106,11 @@ def test_large_batch_goes_through_dense_copy():
     assert float((Y.float() - ref).norm() / ref.norm()) < 5e-3
 
 
-@pytest.mark.parametrize("shape", [(257, 1000, 0.3), (64, 4096, 0.02), (1000, 33, 0.5), (5, 40000, 0.001)])
+@pytest.mark.parametrize("shape", [(257, 1000, 0.3), (64, 4096, 0.02), (1000, 33, 0.5), (5, 40000, 0.001), (300, 4099, 0.9), (40, 11008, 0.5),
+                                   (3, 130000, 0.01)])
 def test_decompress_bit_exact_against_oracle(shape):
+    # rows of up to about 116 000 columns are assembled whole in shared memory by one CTA (several passes of 2048
+    # stored elements for the dense 4099-column case); wider rows take the warp-per-row kernel with a window
     rows, cols, d = shape
     M = workloads.bernoulli_matrix(rows, cols, d, seed=rows * 3 + cols, device=DEV)
     M[0] = 0                                  # an empty row
