@@ -367,6 +367,11 @@ int macko_peer_forward(void *const *peer_y, int64_t row_offset, int64_t rows, ui
  *   pending + p * pending_stride elements; fp32 sum in that order, rounded once; n_pending may be 0), then
  *   out[i] = x[i] * rsqrt(mean(x^2) + eps) * weight[i]. x is updated in place; out must not alias x. `weight`
  *   is read ahead of stream order (a parameter: it must not be written by work still in flight on `stream`).
+ * macko_decode_add_rmsnorm_peer: the same with `pending` = the full-y buffer of a row-sharded product launched
+ *   with MACKO_SCATTER_DEFERRED_WAIT (macko_spmv_fp16_scatter_ex): the kernel itself waits, bounded by
+ *   `spin_limit` polls (0 = default), until the arrival counters of all `world` ranks in `local_flags` (this
+ *   rank's flag words) have reached the rank's call counter, what macko_peer_wait does as a kernel of its own;
+ *   a rank that never arrives is recorded in local_flags[world + 2] and the kernel carries on.
  * macko_decode_rope_attention: qkv = [3][heads][head_dim] (q, k, v of the new token); rotary embedding
  *   (rotate-half convention, tables [max_len][head_dim] with both halves equal) of q and k at *position
  *   (an int64 on the device, clamped into [0, max_len)), k and v stored into row *position of the caches
@@ -379,6 +384,9 @@ int macko_peer_forward(void *const *peer_y, int64_t row_offset, int64_t rows, ui
  */
 int macko_decode_add_rmsnorm(void *x, const void *pending, int n_pending, int64_t pending_stride, const void *weight,
                              void *out, int64_t n, float eps, void *stream);
+int macko_decode_add_rmsnorm_peer(void *x, const void *pending, int n_pending, int64_t pending_stride, const void *weight,
+                                  void *out, int64_t n, float eps, uint32_t *local_flags, int world, uint32_t spin_limit,
+                                  void *stream);
 int macko_decode_rope_attention(const void *qkv, const void *cos_table, const void *sin_table, const int64_t *position,
                                 void *k_cache, void *v_cache, void *out, int heads, int head_dim, int max_len, void *stream);
 int macko_decode_silu_mul(const void *gate_up, void *out, int64_t n, void *stream);

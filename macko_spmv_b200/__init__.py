@@ -101,6 +101,11 @@ def _add_rmsnorm_fake(x, pending, weight, eps):
     return torch.empty_like(x)
 
 
+@torch.library.register_fake("macko_spmv::add_rmsnorm_peer")
+def _add_rmsnorm_peer_fake(x, pending, weight, eps, flags_address, world, spin_limit):
+    return torch.empty_like(x)
+
+
 @torch.library.register_fake("macko_spmv::rope_attention")
 def _rope_attention_fake(qkv, cos_table, sin_table, position, k_cache, v_cache):
     return qkv.new_empty((qkv.numel() // 3,))

@@ -71,6 +71,7 @@ SIGNATURES = {
     "macko_peer_wait_limited": (_int, [_vp, _int, _u32, _vp]),
     "macko_peer_forward": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp]),
     "macko_decode_add_rmsnorm": (_int, [_vp, _vp, _int, _i64, _vp, _vp, _i64, _f, _vp]),
+    "macko_decode_add_rmsnorm_peer": (_int, [_vp, _vp, _int, _i64, _vp, _vp, _i64, _f, _vp, _int, _u32, _vp]),
     "macko_decode_rope_attention": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _vp]),
     "macko_decode_silu_mul": (_int, [_vp, _vp, _i64, _vp]),
     "macko_decode_argmax": (_int, [_vp, _i64, _vp, _vp]),

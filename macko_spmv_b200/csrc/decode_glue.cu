@@ -47,10 +47,12 @@ __device__ __forceinline__ float block_sum(float v, float *scratch)
 // (fp32 sum in that order, rounded to fp16 once), then out[i] = x[i] * rsqrt(mean(x^2) + eps) * weight[i]
 // with the rounded x, all in fp32, rounded to fp16. n_pending may be 0. The weight (a parameter, not the output
 // of the kernel in front) is fetched before the wait for that kernel; a thread keeps its first eight elements
-// in registers between the two passes (all of them when n <= 4096).
+// in registers between the two passes (all of them when n <= 4096). With `peer_flags` the kernel first waits
+// (bounded) for the slices of the other ranks in `pending`.
 __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ pending, int n_pending, long long pending_stride,
-                   const __half *__restrict__ weight, __half *__restrict__ out, int n, float eps)
+                   const __half *__restrict__ weight, __half *__restrict__ out, int n, float eps,
+                   unsigned *__restrict__ peer_flags, int world, unsigned spin_limit)
 {
     __shared__ float scratch[32];
     const bool vec = (n & 7) == 0 && (pending_stride & 7) == 0 &&
@@ -61,6 +63,23 @@ add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ pending, i
     uint4 w_first = make_uint4(0u, 0u, 0u, 0u);
     if ((int)threadIdx.x < n_vec) w_first = __ldg(reinterpret_cast<const uint4 *>(weight) + threadIdx.x);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (peer_flags != nullptr) {
+        // `pending` is the exchange buffer of a row-sharded product launched with a deferred wait: the slices of
+        // the other ranks are complete once their arrival counters have reached this rank's call counter (what
+        // macko_peer_wait checks as a kernel of its own). Bounded: a rank that never arrives is recorded in
+        // flags[world + 2] and the kernel carries on with what is there.
+        if ((int)threadIdx.x < world) {
+            const unsigned seq = peer_flags[world];
+            unsigned seen = 0u;
+            bool arrived = false;
+            for (unsigned spin = 0; spin < spin_limit; ++spin) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(peer_flags + threadIdx.x) : "memory");
+                if ((int)(seen - seq) >= 0) { arrived = true; break; }
+            }
+            if (!arrived) peer_flags[world + 2] = 1u + threadIdx.x;
+        }
+        __syncthreads();
+    }
     float sq = 0.f;
     uint4 x_first = make_uint4(0u, 0u, 0u, 0u);
     if (vec) {
@@ -421,8 +440,9 @@ using namespace macko;
 
 extern "C" {
 
-int macko_decode_add_rmsnorm(void *x, const void *pending, int n_pending, int64_t pending_stride, const void *weight,
-                             void *out, int64_t n, float eps, void *stream)
+static int add_rmsnorm_checked(void *x, const void *pending, int n_pending, int64_t pending_stride, const void *weight,
+                               void *out, int64_t n, float eps, uint32_t *peer_flags, int world, uint32_t spin_limit,
+                               void *stream)
 {
     if (!x || !weight || !out || n <= 0 || n > (1 << 24) || n_pending < 0 || n_pending > 64 || (n_pending > 0 && !pending) ||
         (n_pending > 0 && pending_stride < n))
@@ -430,7 +450,23 @@ int macko_decode_add_rmsnorm(void *x, const void *pending, int n_pending, int64_
                     (long long)n, n_pending, (long long)pending_stride);
     return launch_pdl("add_rmsnorm", add_rmsnorm_kernel, dim3(1), dim3(kNormThreads), 1, static_cast<cudaStream_t>(stream),
                       static_cast<__half *>(x), static_cast<const __half *>(pending), n_pending, (long long)pending_stride,
-                      static_cast<const __half *>(weight), static_cast<__half *>(out), (int)n, eps);
+                      static_cast<const __half *>(weight), static_cast<__half *>(out), (int)n, eps,
+                      reinterpret_cast<unsigned *>(peer_flags), world, (unsigned)(spin_limit == 0 ? (1u << 23) : spin_limit));
+}
+
+int macko_decode_add_rmsnorm(void *x, const void *pending, int n_pending, int64_t pending_stride, const void *weight,
+                             void *out, int64_t n, float eps, void *stream)
+{
+    return add_rmsnorm_checked(x, pending, n_pending, pending_stride, weight, out, n, eps, nullptr, 0, 0, stream);
+}
+
+int macko_decode_add_rmsnorm_peer(void *x, const void *pending, int n_pending, int64_t pending_stride, const void *weight,
+                                  void *out, int64_t n, float eps, uint32_t *local_flags, int world, uint32_t spin_limit,
+                                  void *stream)
+{
+    if (!local_flags || world < 1 || world > 8 || !aligned(local_flags, 4))
+        return fail(MACKO_ERR_INVALID_ARGUMENT, "add_rmsnorm_peer: null or misaligned flags, or world %d outside 1..8", world);
+    return add_rmsnorm_checked(x, pending, n_pending, pending_stride, weight, out, n, eps, local_flags, world, spin_limit, stream);
 }
 
 int macko_decode_silu_mul(const void *gate_up, void *out, int64_t n, void *stream)

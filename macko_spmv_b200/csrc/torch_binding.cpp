@@ -271,8 +271,26 @@ void check_half_vec(const at::Tensor &t, const char *name)
     TORCH_CHECK(t.is_cuda() && t.dtype() == at::kHalf && t.is_contiguous(), name, " must be a contiguous CUDA fp16 tensor");
 }
 
+at::Tensor add_rmsnorm_impl(at::Tensor x, const at::Tensor &pending, const at::Tensor &weight, double eps,
+                            int64_t flags_address, int64_t world, int64_t spin_limit);
+
 // x[n] += rows of pending[k, n] (k may be 0); returns rmsnorm(x) * weight
 at::Tensor add_rmsnorm_cuda(at::Tensor x, const at::Tensor &pending, const at::Tensor &weight, double eps)
+{
+    return add_rmsnorm_impl(x, pending, weight, eps, 0, 0, 0);
+}
+
+// The same with the bounded wait for the other ranks' slices of `pending` inside the kernel; `flags_address` is the
+// device address of this rank's flag words (sharded.PeerGather keeps it).
+at::Tensor add_rmsnorm_peer_cuda(at::Tensor x, const at::Tensor &pending, const at::Tensor &weight, double eps,
+                                 int64_t flags_address, int64_t world, int64_t spin_limit)
+{
+    TORCH_CHECK(flags_address != 0 && world >= 1, "add_rmsnorm_peer needs the flag words of the exchange");
+    return add_rmsnorm_impl(x, pending, weight, eps, flags_address, world, spin_limit);
+}
+
+at::Tensor add_rmsnorm_impl(at::Tensor x, const at::Tensor &pending, const at::Tensor &weight, double eps,
+                            int64_t flags_address, int64_t world, int64_t spin_limit)
 {
     check_half_vec(x, "x");
     check_half_vec(weight, "weight");
@@ -283,9 +301,16 @@ at::Tensor add_rmsnorm_cuda(at::Tensor x, const at::Tensor &pending, const at::T
     const c10::cuda::CUDAGuard guard(x.device());
     at::Tensor out = at::empty_like(x);
     const int k = (int)pending.size(0);
-    check_status(macko_decode_add_rmsnorm(x.data_ptr(), k ? pending.data_ptr() : nullptr, k, x.size(0), weight.data_ptr(),
-                                          out.data_ptr(), x.size(0), (float)eps, c10::cuda::getCurrentCUDAStream()),
-                 "macko_decode_add_rmsnorm");
+    if (flags_address != 0)
+        check_status(macko_decode_add_rmsnorm_peer(x.data_ptr(), k ? pending.data_ptr() : nullptr, k, x.size(0), weight.data_ptr(),
+                                                   out.data_ptr(), x.size(0), (float)eps,
+                                                   reinterpret_cast<uint32_t *>(static_cast<uintptr_t>(flags_address)), (int)world,
+                                                   (uint32_t)spin_limit, c10::cuda::getCurrentCUDAStream()),
+                     "macko_decode_add_rmsnorm_peer");
+    else
+        check_status(macko_decode_add_rmsnorm(x.data_ptr(), k ? pending.data_ptr() : nullptr, k, x.size(0), weight.data_ptr(),
+                                              out.data_ptr(), x.size(0), (float)eps, c10::cuda::getCurrentCUDAStream()),
+                     "macko_decode_add_rmsnorm");
     return out;
 }
 
@@ -353,6 +378,8 @@ TORCH_LIBRARY(macko_spmv, m)
     m.def("multiply_planned(Tensor M_values, Tensor M_deltas, Tensor M_row_indices, int M_rows, int M_cols, Tensor plan, "
           "int virtual_rows, int segment_elements, int split_rows, Tensor V, bool frozen) -> Tensor");
     m.def("add_rmsnorm(Tensor(a!) x, Tensor pending, Tensor weight, float eps) -> Tensor");
+    m.def("add_rmsnorm_peer(Tensor(a!) x, Tensor pending, Tensor weight, float eps, int flags_address, int world, "
+          "int spin_limit) -> Tensor");
     m.def("rope_attention(Tensor qkv, Tensor cos_table, Tensor sin_table, Tensor position, Tensor(a!) k_cache, "
           "Tensor(b!) v_cache) -> Tensor");
     m.def("silu_mul(Tensor gate_up) -> Tensor");
@@ -371,6 +398,7 @@ TORCH_LIBRARY_IMPL(macko_spmv, CUDA, m)
     m.impl("plan_build", &plan_build_cuda);
     m.impl("multiply_planned", &multiply_planned_cuda);
     m.impl("add_rmsnorm", &add_rmsnorm_cuda);
+    m.impl("add_rmsnorm_peer", &add_rmsnorm_peer_cuda);
     m.impl("rope_attention", &rope_attention_cuda);
     m.impl("silu_mul", &silu_mul_cuda);
     m.impl("argmax", &argmax_cuda);

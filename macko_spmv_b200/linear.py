@@ -165,13 +165,15 @@ class ColumnShardedMackoLinear(nn.Module):
         torch.cuda.synchronize(values.device)   # the compressor has finished: the block is final from here on
         self._c0_ptr = values.data_ptr()
 
-    def partials(self, x_local: torch.Tensor) -> torch.Tensor:
+    def partials(self, x_local: torch.Tensor, defer_wait: bool = False) -> torch.Tensor:
         """The N partial output vectors [N, out] (rank order), not yet added: a view of the exchange slot, to be
-        consumed (in stream order) before the second-next product through the same `PeerGather`."""
+        consumed (in stream order) before the second-next product through the same `PeerGather`.
+        `defer_wait`: the rows of the other ranks are complete only behind a wait on the exchange's flag words
+        (`torch.ops.macko_spmv.add_rmsnorm_peer` does it itself)."""
         if x_local.dim() != 1 or x_local.shape[0] != self.in_local:
             raise RuntimeError(f"expected this rank's {self.in_local} input features, got {tuple(x_local.shape)}")
         final = self.c_0.data_ptr() == self._c0_ptr
-        parts = self.peer.multiply(self.shard, x_local.contiguous(), immutable=final)
+        parts = self.peer.multiply(self.shard, x_local.contiguous(), immutable=final, defer_wait=defer_wait)
         return parts.view(self.peer.world, self.out_features)
 
     def forward(self, x_local: torch.Tensor) -> torch.Tensor:

@@ -140,12 +140,12 @@ class Block(nn.Module):
     def step_fused(self, x, pending, pos, cos_table, sin_table):
         """The same block as `forward` with three kernels of this package between the four products. `x` [hidden]
         is the residual stream, updated in place; `pending` [k, hidden] holds output vectors that have not been
-        added to it yet (the previous block's down projection: one vector, or one partial vector per rank).
-        Returns this block's own pending output."""
+        added to it yet (the previous block's down projection: one vector, or one partial vector per rank), as
+        the pair that `_pending_output` returns. Returns this block's own pending output."""
         ops = torch.ops.macko_spmv
-        qkv = self.qkv_proj(ops.add_rmsnorm(x, pending, self.input_norm.weight, self.input_norm.eps))
+        qkv = self.qkv_proj(_add_norm(x, pending, self.input_norm))
         attn = ops.rope_attention(qkv, cos_table, sin_table, pos, self.k_cache, self.v_cache)
-        gu = self.gate_up_proj(ops.add_rmsnorm(x, _pending_output(self.o_proj, attn), self.post_norm.weight, self.post_norm.eps))
+        gu = self.gate_up_proj(_add_norm(x, _pending_output(self.o_proj, attn), self.post_norm))
         return _pending_output(self.down_proj, ops.silu_mul(gu))
 
     def prefill(self, x, cos, sin):
@@ -165,11 +165,21 @@ class Block(nn.Module):
 
 
 def _pending_output(layer, x):
-    """The output of a projection as rows still to be added to the residual stream: [1, out], or the [N, out]
-    partial vectors of a column-sharded layer (left in the exchange buffer: the next kernel adds them up)."""
+    """The output of a projection as rows still to be added to the residual stream, with the exchange they wait
+    for: ([1, out], None), or ([N, out], peer) for the partial vectors of a column-sharded layer, which stay in
+    the exchange buffer; the product kernel has only published this rank's row, and the kernel that adds the rows
+    up waits for the other ranks itself."""
     if isinstance(layer, ColumnShardedMackoLinear):
-        return layer.partials(x)
-    return layer(x).view(1, -1)
+        return layer.partials(x, defer_wait=True), layer.peer
+    return layer(x).view(1, -1), None
+
+
+def _add_norm(x, pending, norm):
+    """x += the pending rows; returns rmsnorm(x) * weight (one kernel; with an exchange pending, its wait too)."""
+    rows, peer = pending
+    if peer is None:
+        return torch.ops.macko_spmv.add_rmsnorm(x, rows, norm.weight, norm.eps)
+    return torch.ops.macko_spmv.add_rmsnorm_peer(x, rows, norm.weight, norm.eps, peer.flags_address, peer.world, peer.spin_limit)
 
 
 def _rope(t, cos, sin):
@@ -227,10 +237,10 @@ class LlamaDecoder(nn.Module):
         """fp16 logits [vocab] of the token at position `pos`; updates the KV cache."""
         x = self.embed.index_select(0, token)[0]
         if self.fused_glue:
-            pending = x.new_empty((0, x.shape[0]))
+            pending = (x.new_empty((0, x.shape[0])), None)
             for blk in self.blocks:
                 pending = blk.step_fused(x, pending, pos, self.cos_table, self.sin_table)
-            return self.lm_head(torch.ops.macko_spmv.add_rmsnorm(x, pending, self.norm.weight, self.norm.eps))
+            return self.lm_head(_add_norm(x, pending, self.norm))
         cos = self.cos_table.index_select(0, pos)[0]
         sin = self.sin_table.index_select(0, pos)[0]
         mask = torch.where(self.positions <= pos, self.zero, self.neg_inf).view(1, 1, 1, -1)

@@ -199,9 +199,12 @@ class PeerGather:
             comp[0].data_ptr(), comp[1].data_ptr(), comp[2].data_ptr(), comp[3], comp[4], comp[0].numel(),
             x.data_ptr(), table, shard.row_lo, self._flag_table, self.rank, self.world, flags, self.spin_limit, stream))
 
-    def multiply(self, shard: RowShard, x: torch.Tensor, immutable: bool = False, slot: int | None = None) -> torch.Tensor:
+    def multiply(self, shard: RowShard, x: torch.Tensor, immutable: bool = False, slot: int | None = None,
+                 defer_wait: bool = False) -> torch.Tensor:
         """Full y (a view of the current slot, length shard.total_rows) after all ranks delivered.
         `immutable`: the shard's buffers are final (weights), see MACKO_SPMV_MATRIX_IMMUTABLE.
+        `defer_wait`: the kernel publishes this rank's slice and returns; the reader of the view waits for the
+        other ranks itself (`wait()`, or a kernel that takes `flags_address`, like `add_rmsnorm_peer`).
         `slot`: None = the two alternating slots; 2 = the spare slot (see the class description)."""
         if shard.total_rows > self.max_rows:
             raise ValueError(f"matrix has {shard.total_rows} rows, the exchange buffers hold {self.max_rows}")
@@ -210,7 +213,8 @@ class PeerGather:
             self._slot ^= 1
         elif slot not in (0, 1, 2):
             raise ValueError("slot must be 0, 1 or 2")
-        self._launch(shard, x, self._table(slot, 0), self._cabi.SPMV_MATRIX_IMMUTABLE if immutable else 0)
+        self._launch(shard, x, self._table(slot, 0), (self._cabi.SPMV_MATRIX_IMMUTABLE if immutable else 0) |
+                     (self._cabi.SCATTER_DEFERRED_WAIT if defer_wait else 0))
         # the kernel itself returns only after the slices of all ranks have landed (its last CTA waits)
         return self.buf[slot, : shard.total_rows]
 
@@ -252,6 +256,11 @@ class PeerGather:
             main.wait_stream(self._side)   # the forwards of this step (joins the side branch when captured)
             self._side_busy = False
         self.check(self.lib, self.lib.macko_peer_wait_limited(self._local_flags, self.world, self.spin_limit, main.cuda_stream))
+
+    @property
+    def flags_address(self) -> int:
+        """Device address of this rank's flag words, for kernels that wait for the exchange themselves."""
+        return self._local_flags
 
     def error_flag(self) -> int:
         """0, or 1 + the rank whose slice never arrived in some earlier wait (reads device memory)."""

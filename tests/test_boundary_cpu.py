@@ -162,6 +162,8 @@ def test_new_entry_points_validate_before_touching_the_device():
     assert lib.macko_decode_add_rmsnorm(a16, None, 1, 64, a16, a16, 64, 1e-5, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_decode_add_rmsnorm(a16, a16, 2, 32, a16, a16, 64, 1e-5, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_decode_add_rmsnorm(a16, None, 0, 0, a16, a16, 0, 1e-5, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_decode_add_rmsnorm_peer(a16, a16, 2, 64, a16, a16, 64, 1e-5, None, 2, 0, None) == cabi.ERR_INVALID_ARGUMENT
+    assert lib.macko_decode_add_rmsnorm_peer(a16, a16, 2, 64, a16, a16, 64, 1e-5, a16, 9, 0, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_decode_silu_mul(a16, None, 64, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_decode_argmax(a16, 0, a16, None) == cabi.ERR_INVALID_ARGUMENT
     assert lib.macko_decode_rope_attention(a16, a16, a16, a16, a16, a16, a16, 4, 96, 16, None) == cabi.ERR_INVALID_ARGUMENT

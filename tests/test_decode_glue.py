@@ -130,3 +130,30 @@ def test_argmax(n):
     assert int(ops.argmax(v)) == (n // 2 if n > 1 else 0)
     v.fill_(float("-inf"))
     assert int(ops.argmax(v)) == 0
+
+
+def test_add_rmsnorm_peer_wait_is_bounded_and_says_who_was_missing():
+    """The kernel that adds up the partial rows of a column-sharded layer waits for the other ranks itself: with
+    an arrival counter that never comes the wait runs out after `spin_limit` polls, records the rank, and the
+    kernel still produces its result; with all counters there nothing is recorded."""
+    n, world = 256, 2
+    g = _gen(9)
+    x0 = torch.randn(n, device="cuda", generator=g).half()
+    pending = torch.randn(world, n, device="cuda", generator=g).half()
+    w = torch.ones(n, dtype=torch.float16, device="cuda")
+    xr = x0.clone()
+    ref = ops.add_rmsnorm(xr, pending, w, 1e-5)
+    flags = torch.zeros(world + 3 + 13, dtype=torch.int32, device="cuda")
+    flags[world] = 1          # this rank has issued one exchange
+    flags[0] = 1              # rank 0 (itself) has delivered it, rank 1 has not
+    xa = x0.clone()
+    out = ops.add_rmsnorm_peer(xa, pending, w, 1e-5, flags.data_ptr(), world, 1000)
+    torch.cuda.synchronize()
+    assert int(flags[world + 2]) == 2
+    assert torch.equal(out, ref) and torch.equal(xa, xr)
+    flags[world + 2] = 0
+    flags[1] = 1
+    xb = x0.clone()
+    out = ops.add_rmsnorm_peer(xb, pending, w, 1e-5, flags.data_ptr(), world, 1000)
+    torch.cuda.synchronize()
+    assert int(flags[world + 2]) == 0 and torch.equal(out, ref)
