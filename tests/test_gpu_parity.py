@@ -106,6 +106,31 @@ def test_compress_random_against_oracle(shape):
         _assert_buffers_equal(macko_spmv.compress(Mo), exp, f"{shape} d={dens} unaligned")
 
 
+def test_compress_emit_into_a_2_byte_aligned_values_buffer():
+    """`values` needs 2-byte alignment only: at an address that is not a multiple of 16 the emit kernel stores the
+    values of a group one by one instead of as one 16-byte store; same bits."""
+    lib = cabi.load()
+    rows, cols = 300, 1999
+    g = torch.Generator().manual_seed(5)
+    M = torch.randn(rows, cols, generator=g).half()
+    M[torch.rand(rows, cols, generator=g) > 0.3] = 0
+    M = M.to(_dev())
+    stream = torch.cuda.current_stream().cuda_stream
+    ri = torch.empty(rows + 1, dtype=torch.int32, device=M.device)
+    cabi.check(lib, lib.macko_compress_count(M.data_ptr(), rows, cols, ri.data_ptr(), stream))
+    P = (int(ri[rows].item()) + 7) // 8 * 8
+    backing = torch.full((P + 8,), 0x5A5A, dtype=torch.int16, device=M.device)
+    values = backing[1 : P + 1]
+    assert values.data_ptr() % 16 == 2
+    deltas = torch.full((P // 2,), 0xA5, dtype=torch.uint8, device=M.device)
+    ws = torch.empty(lib.macko_compress_workspace_bytes(P), dtype=torch.uint8, device=M.device)
+    cabi.check(lib, lib.macko_compress_emit(M.data_ptr(), rows, cols, ri.data_ptr(), P, values.data_ptr(),
+                                            deltas.data_ptr(), ws.data_ptr(), ws.numel(), stream))
+    exp = oracle.compress(_u16(M).reshape(rows, cols))
+    _assert_buffers_equal((values.view(torch.float16), deltas, ri, rows, cols), exp, "2-byte-aligned values")
+    assert int(backing[0]) == 0x5A5A and bool((backing[P + 1:] == 0x5A5A).all())
+
+
 def test_compress_full_size_checksum():
     # a full-size layer: bit-exact against the oracle, and the decode property M e_j = M[:, j]
     rows, cols = 11008, 4096
