@@ -101,6 +101,13 @@ class ClockSampler:
             out = ""
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        if not out.strip():
+            # the loop never got to print (a very short run): one query now, right behind the load
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=10).stdout
+            except Exception:
+                out = ""
         for line in out.strip().splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 8:
@@ -729,13 +736,15 @@ def run_own_arm(args):
         graphs = None
         run_step = lambda i: step_device()
     used_graph = graphs is not None
+    # the sampler starts in front of the warm-up steps (the same load): nvidia-smi needs some tens of
+    # milliseconds before its first line, more than the timed region lasts
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for i in range(max(args.warmup, 3)):
         run_step(i)
     torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
