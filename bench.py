@@ -516,7 +516,10 @@ def batched_leg(device):
     out["single_us"] = timed(lambda: macko_spmv.multiply(comp, V[0]))
     for b in (2, 4, 8, 16):
         Vb = V[:b].contiguous()
-        out[f"batched_{b}_us"] = timed(lambda: macko_spmv.multiply_batched(comp, Vb))
+        out[f"batched_{b}_us"] = timed(lambda: macko_spmv.multiply_batched(comp, Vb))   # the API's own routing
+    V16 = V[:16].contiguous()
+    out["two_passes_16_us"] = timed(lambda: torch.ops.macko_spmv.multiply_batched.default(*comp[:5], V16))
+    out["dense_route_16_us"] = timed(lambda: V16 @ macko_spmv.decompress(comp).t())
     V8 = V[:8].contiguous()
     out["loop_of_8_us"] = timed(lambda: [macko_spmv.multiply(comp, V8[i]) for i in range(8)])
     out["prefill_128_dense_route_us"] = timed(lambda: macko_spmv.multiply_batched(comp, V))

@@ -222,9 +222,23 @@ def multiply(compressed_M, V, out=None):
     )
 
 
-# Above this many right-hand sides a dense copy of the matrix plus one tensor-core GEMM is cheaper than
-# streaming the compressed matrix once per 8 vectors.
+# Above this many right-hand sides a dense copy of the matrix plus one tensor-core GEMM is always cheaper than
+# streaming the compressed matrix once per 8 vectors; from 9 vectors on (two passes) it depends on the density.
 DENSE_BATCH_THRESHOLD = 16
+
+
+def _dense_copy_pays(compressed_M, batch: int) -> bool:
+    """9..DENSE_BATCH_THRESHOLD vectors of an fp16 matrix: passes of the multi-vector kernel (8 vectors each, measured
+    at 1.3 TB/s of compressed bytes) against one decompression (3.0 TB/s of compressed + dense bytes) plus about
+    10 us for the GEMM and the dense buffer. At 50 % density the dense copy wins from 9 vectors on (59 against
+    85 us on 11008x4096), at 10 % the two passes do."""
+    if batch <= 8 or compressed_M[0].dtype != torch.float16:
+        return False
+    stored_bytes = 2.5 * compressed_M[0].numel()
+    passes = (batch + 7) // 8
+    multi_vector_us = passes * stored_bytes / 1.3e6
+    dense_us = (stored_bytes + 2.0 * compressed_M[3] * compressed_M[4]) / 3.0e6 + 10.0
+    return dense_us < multi_vector_us
 
 
 def decompress(compressed_M):
@@ -237,15 +251,16 @@ def multiply_batched(compressed_M, V):
     """Y[batch, rows] = V[batch, cols] @ M^T for a compressed matrix and fp16 CUDA vectors.
 
     The reference runs batched inputs as a loop of `multiply` calls (torch.vmap fallback,
-    python_scripts/util_run_pruned_llm.py:112-115). Here 2..DENSE_BATCH_THRESHOLD vectors share passes
-    over the compressed matrix (8 per pass); larger batches decompress once and run a dense GEMM.
+    python_scripts/util_run_pruned_llm.py:112-115). Here up to 8 vectors share one pass over the compressed
+    matrix; 9..DENSE_BATCH_THRESHOLD take two passes or, where the matrix is dense enough for that to be cheaper,
+    the route of the larger batches: decompress once and run a dense GEMM.
     """
     assert compressed_M[0].is_cuda
     assert V.is_cuda
     assert V.is_contiguous()
     if V.dim() != 2:
         raise RuntimeError("V must have shape [batch, cols]")
-    if V.shape[0] > DENSE_BATCH_THRESHOLD:
+    if V.shape[0] > DENSE_BATCH_THRESHOLD or _dense_copy_pays(compressed_M, V.shape[0]):
         return V @ decompress(compressed_M).t()
     return torch.ops.macko_spmv.multiply_batched.default(*compressed_M[:5], V)
 
