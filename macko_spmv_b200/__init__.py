@@ -230,14 +230,14 @@ DENSE_BATCH_THRESHOLD = 16
 def _dense_copy_pays(compressed_M, batch: int) -> bool:
     """9..DENSE_BATCH_THRESHOLD vectors of an fp16 matrix: passes of the multi-vector kernel (8 vectors each, measured
     at 1.3 TB/s of compressed bytes) against one decompression (3.0 TB/s of compressed + dense bytes) plus about
-    10 us for the GEMM and the dense buffer. At 50 % density the dense copy wins from 9 vectors on (59 against
-    85 us on 11008x4096), at 10 % the two passes do."""
+    19 us for the GEMM and the dense buffer. At 50 % density the dense copy wins from 9 vectors on (68 against
+    85 us for 16 vectors on 11008x4096), at 30 % and below the two passes do."""
     if batch <= 8 or compressed_M[0].dtype != torch.float16:
         return False
     stored_bytes = 2.5 * compressed_M[0].numel()
     passes = (batch + 7) // 8
     multi_vector_us = passes * stored_bytes / 1.3e6
-    dense_us = (stored_bytes + 2.0 * compressed_M[3] * compressed_M[4]) / 3.0e6 + 10.0
+    dense_us = (stored_bytes + 2.0 * compressed_M[3] * compressed_M[4]) / 3.0e6 + 19.0
     return dense_us < multi_vector_us
 
 
