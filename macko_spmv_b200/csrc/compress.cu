@@ -45,27 +45,27 @@ __device__ __forceinline__ unsigned short canonical(unsigned short h, unsigned n
 // Loads the 8 fp16 of this lane for the step starting at global element index g0 (a multiple of 8
 // relative to the allocation start on the vector path) as four packed words; elements outside the
 // allocation read as zero. Which of the 8 belong to the row is decided by row_bits().
-__device__ __forceinline__ void load8(const unsigned short *dense, long long g0, long long total, bool vec_ok,
+__device__ __forceinline__ void load8(const unsigned short *dense, unsigned g0, unsigned total, bool vec_ok,
                                       unsigned (&w)[4])
 {
-    if (vec_ok && g0 >= 0 && g0 + 8 <= total) {
+    if (vec_ok && g0 + 8u <= total) {
         const uint4 v = __ldg(reinterpret_cast<const uint4 *>(dense + g0));
         w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
     } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const long long g = g0 + 2 * j;
-            const unsigned lo16 = (g >= 0 && g < total) ? (unsigned)__ldg(dense + g) : 0u;
-            const unsigned hi16 = (g + 1 >= 0 && g + 1 < total) ? (unsigned)__ldg(dense + g + 1) : 0u;
+            const unsigned g = g0 + 2u * j;
+            const unsigned lo16 = g < total ? (unsigned)__ldg(dense + g) : 0u;
+            const unsigned hi16 = g + 1u < total ? (unsigned)__ldg(dense + g + 1u) : 0u;
             w[j] = lo16 | (hi16 << 16);
         }
     }
 }
 
 // Bit i set <=> element g0 + i lies inside the row [lo, hi).
-__device__ __forceinline__ unsigned row_bits(long long g0, long long lo, long long hi)
+__device__ __forceinline__ unsigned row_bits(unsigned g0, unsigned lo, unsigned hi)
 {
-    const int a = (int)min(max(lo - g0, 0LL), 8LL), b = (int)min(max(hi - g0, 0LL), 8LL);
+    const unsigned a = g0 >= lo ? 0u : min(lo - g0, 8u), b = g0 >= hi ? 0u : min(hi - g0, 8u);
     return ((1u << b) - 1u) & ~((1u << a) - 1u);
 }
 
@@ -103,11 +103,13 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const long long total = (long long)rows * cols;
-    const long long row_lo = (long long)row * cols;
-    const long long row_hi = row_lo + cols;
+    // element indices fit 32 bits: the entry points refuse matrices of 2^31 elements or more, and a walk ends
+    // less than 2048 elements behind its row
+    const unsigned total = (unsigned)rows * (unsigned)cols;
+    const unsigned row_lo = (unsigned)row * (unsigned)cols;
+    const unsigned row_hi = row_lo + (unsigned)cols;
     // First step starts at the 8-element boundary at or below the row start.
-    const long long first = vec_ok ? (row_lo & ~7LL) : row_lo;
+    const unsigned first = vec_ok ? (row_lo & ~7u) : row_lo;
 
     int carry_prev = -1;   // column of the last non-zero seen so far in this row
     int count = 0;         // !EMIT: stored elements seen by this lane
@@ -123,15 +125,15 @@ compress_rows_kernel(const unsigned short *__restrict__ dense, int rows, int col
     __shared__ unsigned char stage_n[EMIT ? kWarpsPerCta : 1][EMIT ? kStageElems : 1];
     const int wslot = EMIT ? (int)(threadIdx.x >> 5) : 0;
 
-    for (long long group0 = first; group0 < row_hi; group0 += (long long)kUnroll * kColsPerStep) {
+    for (unsigned group0 = first; group0 < row_hi; group0 += (unsigned)(kUnroll * kColsPerStep)) {
         // all loads of kUnroll steps are issued before the first one is consumed
         unsigned ws[kUnroll][4];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
-            load8(dense, group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane, total, vec_ok, ws[u]);
+            load8(dense, group0 + (unsigned)(u * kColsPerStep + lane * kColsPerLane), total, vec_ok, ws[u]);
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const long long g0 = group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane;
+            const unsigned g0 = group0 + (unsigned)(u * kColsPerStep + lane * kColsPerLane);
             const unsigned (&w)[4] = ws[u];
             const int c0 = (int)(g0 - row_lo);  // column of element 0; may be negative on the first step
             const unsigned nz = nonzero_bits(w) & row_bits(g0, row_lo, row_hi);
@@ -305,10 +307,12 @@ emit_rows_packed_kernel(const unsigned short *__restrict__ dense, int rows, int 
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const long long total = (long long)rows * cols;
-    const long long row_lo = (long long)row * cols;
-    const long long row_hi = row_lo + cols;
-    const long long first = vec_ok ? (row_lo & ~7LL) : row_lo;
+    // element indices fit 32 bits: the entry points refuse matrices of 2^31 elements or more, and a walk ends
+    // less than 2048 elements behind its row
+    const unsigned total = (unsigned)rows * (unsigned)cols;
+    const unsigned row_lo = (unsigned)row * (unsigned)cols;
+    const unsigned row_hi = row_lo + (unsigned)cols;
+    const unsigned first = vec_ok ? (row_lo & ~7u) : row_lo;
 
     EmitRing<unsigned short> ring;
     ring.sv = ring_v[threadIdx.x >> 5];
@@ -320,18 +324,18 @@ emit_rows_packed_kernel(const unsigned short *__restrict__ dense, int rows, int 
     ring.refused = row_indices[row] != out0;
     int carry_prev = -1;   // column of the last non-zero seen so far in this row
 
-    for (long long group0 = first; group0 < row_hi; group0 += (long long)kUnroll * kColsPerStep) {
+    for (unsigned group0 = first; group0 < row_hi; group0 += (unsigned)(kUnroll * kColsPerStep)) {
         unsigned ws[kUnroll][4];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
-            load8(dense, group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane, total, vec_ok, ws[u]);
+            load8(dense, group0 + (unsigned)(u * kColsPerStep + lane * kColsPerLane), total, vec_ok, ws[u]);
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const long long g0 = group0 + (long long)u * kColsPerStep + (long long)lane * kColsPerLane;
+            const unsigned g0 = group0 + (unsigned)(u * kColsPerStep + lane * kColsPerLane);
             const unsigned (&w)[4] = ws[u];
             const int c0 = (int)(g0 - row_lo);  // column of element 0; may be negative on the first step
             unsigned nz = nonzero_bits(w);
-            if (g0 < row_lo || g0 + 8 > row_hi) nz &= row_bits(g0, row_lo, row_hi);
+            if (g0 < row_lo || g0 + 8u > row_hi) nz &= row_bits(g0, row_lo, row_hi);
             const unsigned any = __ballot_sync(0xffffffffu, nz != 0);
             if (any == 0) continue;  // warp-uniform
             const int my_last = c0 + (31 - __clz(nz | 1u));
@@ -479,18 +483,18 @@ pack_kernel(const uint2 *__restrict__ nibbles8, const int *__restrict__ ri, int 
 // two ways: a value is one signed byte, and trailing pads stay: a run of t zeros at the end of a row (or a
 // whole empty row, t = cols) still emits floor(t / 16) pads (value 0, delta 15). Same walk as above, one warp
 // per row, 8 columns per lane and step (one 64-bit load when the matrix is 8-byte aligned).
-__device__ __forceinline__ void load8_bytes(const signed char *dense, long long g0, long long total, bool vec_ok,
+__device__ __forceinline__ void load8_bytes(const signed char *dense, unsigned g0, unsigned total, bool vec_ok,
                                             unsigned (&w)[2])
 {
-    if (vec_ok && g0 >= 0 && g0 + 8 <= total) {
+    if (vec_ok && g0 + 8u <= total) {
         const uint2 v = __ldg(reinterpret_cast<const uint2 *>(dense + g0));
         w[0] = v.x; w[1] = v.y;
     } else {
         w[0] = w[1] = 0u;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const long long g = g0 + j;
-            const unsigned b = (g >= 0 && g < total) ? (unsigned)(unsigned char)__ldg(dense + g) : 0u;
+            const unsigned g = g0 + j;
+            const unsigned b = g < total ? (unsigned)(unsigned char)__ldg(dense + g) : 0u;
             w[j >> 2] |= b << (8 * (j & 3));
         }
     }
@@ -513,16 +517,18 @@ compress_rows_int8_kernel(const signed char *__restrict__ dense, int rows, int c
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const long long total = (long long)rows * cols;
-    const long long row_lo = (long long)row * cols;
-    const long long row_hi = row_lo + cols;
-    const long long first = vec_ok ? (row_lo & ~7LL) : row_lo;
+    // element indices fit 32 bits: the entry points refuse matrices of 2^31 elements or more, and a walk ends
+    // less than 2048 elements behind its row
+    const unsigned total = (unsigned)rows * (unsigned)cols;
+    const unsigned row_lo = (unsigned)row * (unsigned)cols;
+    const unsigned row_hi = row_lo + (unsigned)cols;
+    const unsigned first = vec_ok ? (row_lo & ~7u) : row_lo;
     int carry_prev = -1;
     int count = 0;
     int out = EMIT ? row_indices[row] : 0;
     bool refused = false;
-    for (long long group0 = first; group0 < row_hi; group0 += kColsPerStep) {
-        const long long g0 = group0 + (long long)lane * kColsPerLane;
+    for (unsigned group0 = first; group0 < row_hi; group0 += (unsigned)kColsPerStep) {
+        const unsigned g0 = group0 + (unsigned)(lane * kColsPerLane);
         unsigned w[2];
         load8_bytes(dense, g0, total, vec_ok, w);
         const int c0 = (int)(g0 - row_lo);
