@@ -226,7 +226,10 @@ int64_t macko_compress_workspace_bytes(int64_t padded_count);
  *   row_indices   output of macko_compress_count for the same `dense`
  *   padded_count  P = ceil(ri[rows]/8)*8
  *   workspace     device scratch of macko_compress_workspace_bytes(P) bytes,
- *                 8-byte aligned; contents undefined afterwards
+ *                 8-byte aligned; contents undefined afterwards. The fp16 and
+ *                 bf16 calls check it and leave it alone (they pack the deltas
+ *                 in the same pass, after clearing `deltas` on `stream`); the
+ *                 int8 call writes one delta per byte into it and packs after.
  */
 int macko_compress_emit(const void *dense, int64_t rows, int64_t cols,
                         const int32_t *row_indices, int64_t padded_count,
