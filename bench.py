@@ -526,6 +526,57 @@ def batched_leg(device):
     return out
 
 
+
+# --------------------------------------------------------------------------- value types
+
+def value_types_leg(device, peak_gbs):
+    """The 11008x4096 layer at density 0.5 in the three value types of the format: fp16 (the reference's),
+    bfloat16 (values, x and y) and int8 values with fp16 vectors (the reference's int8 variant). Cold (rotating
+    copies larger than L2), matrices declared immutable, graph replay; microseconds per product and fraction
+    of the measured peak on each type's own algorithmic bytes; y checked against a dense fp32 product."""
+    import macko_spmv_b200 as macko_spmv
+    from macko_spmv_b200 import workloads
+
+    rows, cols = 11008, 4096
+    W = workloads.magnitude_pruned_matrix(rows, cols, 0.5, 2914, device=device)
+    x16 = workloads.dense_vector(cols, 2915, device)
+    out = {"shape": [rows, cols], "density": 0.5}
+    variants = {
+        "fp16": (W, x16),
+        "bf16": (W.to(torch.bfloat16), x16.to(torch.bfloat16)),
+        "int8": (torch.clamp((W.float() * 2000.0).round(), -127, 127).to(torch.int8), x16),
+    }
+    for name, (M, x) in variants.items():
+        comp = macko_spmv.compress(M.contiguous())
+        stored = comp[0].numel()
+        value_bytes = 1 if name == "int8" else 2
+        nbytes = (value_bytes + 0.5) * stored + 4 * (rows + 1) + 2 * cols + 2 * rows
+        ncopy = max(2, int(300e6 / nbytes) + 1)
+        copies = [macko_spmv.freeze(comp, plan=False)] + [
+            macko_spmv.freeze((comp[0].clone(), comp[1].clone(), comp[2].clone(), rows, cols), plan=False) for _ in range(ncopy - 1)]
+        ys = [torch.empty(rows, dtype=x.dtype, device=device) for _ in range(ncopy)]
+
+        def step():
+            for c, y in zip(copies, ys):
+                macko_spmv.multiply(c, x, out=y)
+        g = capture(step)
+        for _ in range(3):
+            g.replay()
+        e0, e1 = event_pair()
+        e0.record()
+        for _ in range(20):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1000.0 / (20 * ncopy)
+        ref = M.float() @ x.float()
+        rel = float((ys[0].float() - ref).norm() / ref.norm())
+        out[name] = {"us": round(us, 2), "algorithmic_bytes": int(nbytes), "roofline_frac": round(nbytes / us / 1e3 / peak_gbs, 4),
+                     "rel_l2_vs_dense_fp32": rel, "y_ok": rel < (2e-2 if name == "bf16" else 5e-3)}
+        del g, copies, ys, comp
+        torch.cuda.empty_cache()
+    return out
+
 # --------------------------------------------------------------------------- decode
 
 def decode_leg(device, world, peer_factory, densities, layers, prompt, new_tokens):
@@ -941,6 +992,9 @@ def run_own_arm(args):
     if single is not None:
         ok = ok and single["y_ok"]
     batched = batched_leg(device) if (world == 1 and not args.no_batched) else None
+    value_types = value_types_leg(device, peak_gbs) if (world == 1 and not args.no_batched) else None
+    if value_types is not None:
+        ok = ok and all(value_types[k]["y_ok"] for k in ("fp16", "bf16", "int8"))
 
     # ---- peer error flag and verdict of the checks, over all ranks ------------------------------
     peer_flag = peer.error_flag() if peer is not None else 0
@@ -1045,6 +1099,8 @@ def run_own_arm(args):
             line["single_4096"] = single
         if batched is not None:
             line["batched"] = batched
+        if value_types is not None:
+            line["value_types"] = value_types
         if per_case is not None:
             line["per_case"] = per_case
             sp = [p["speedup_vs_cublas"] for p in per_case]
