@@ -411,3 +411,34 @@ def test_multiply_against_reference_gpu_kernel():
         ref = M.float() @ x.float()
         assert float((theirs.float() - ref).norm() / ref.norm()) <= REL_L2
         assert float((ours.float() - ref).norm() / ref.norm()) <= REL_L2
+
+
+def test_compress_structured_patterns_against_oracle():
+    """Rows built from runs of zeros and non-zeros of drawn lengths (long pad runs, gaps of exactly 15, 16 and 17
+    zeros, dense stretches, empty rows, a non-zero in the last column), many row widths around the 8- and
+    256-column steps of the walk: compressed buffers bit for bit against the oracle."""
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        rows = int(rng.integers(1, 40))
+        cols = int(rng.choice([1, 7, 8, 9, 15, 16, 17, 31, 255, 256, 257, 511, 1000, 4097, 9000]))
+        M = np.zeros((rows, cols), dtype=np.float16)
+        for r in range(rows):
+            c = 0
+            kind = rng.integers(0, 5)
+            while c < cols:
+                gap = int(rng.choice([0, 1, 14, 15, 16, 17, 31, 32, 33, 255, 256, 300, 5000])) if kind != 0 else cols
+                c += gap
+                run = int(rng.choice([1, 1, 2, 7, 8, 9, 64, 300]))
+                if c < cols:
+                    n = min(run, cols - c)
+                    M[r, c:c + n] = rng.standard_normal(n).astype(np.float16) + np.float16(3.0)
+                    c += n
+            if kind == 1:
+                M[r, cols - 1] = 1.5
+            if kind == 2:
+                M[r, 0] = -2.0
+        neg = rng.random(M.shape) < 0.1
+        M[(M == 0) & neg] = np.float16(-0.0)           # pads take the sign of the zero they sit on
+        exp = oracle.compress(M.view(np.uint16))
+        got = macko_spmv.compress(torch.from_numpy(M).to(_dev()))
+        _assert_buffers_equal(got, exp, f"case {case}: {rows}x{cols}")
