@@ -416,7 +416,8 @@ def test_multiply_against_reference_gpu_kernel():
 def test_compress_structured_patterns_against_oracle():
     """Rows built from runs of zeros and non-zeros of drawn lengths (long pad runs, gaps of exactly 15, 16 and 17
     zeros, dense stretches, empty rows, a non-zero in the last column), many row widths around the 8- and
-    256-column steps of the walk: compressed buffers bit for bit against the oracle."""
+    256-column steps of the walk: compressed buffers bit for bit against the oracle, then decompressed and
+    multiplied."""
     rng = np.random.default_rng(2024)
     for case in range(40):
         rows = int(rng.integers(1, 40))
@@ -442,3 +443,9 @@ def test_compress_structured_patterns_against_oracle():
         exp = oracle.compress(M.view(np.uint16))
         got = macko_spmv.compress(torch.from_numpy(M).to(_dev()))
         _assert_buffers_equal(got, exp, f"case {case}: {rows}x{cols}")
+        # the same buffers back through the decompressor (bit for bit) and the product (tolerance tiers)
+        comp_np = (exp[0], exp[1], exp[2], rows, cols)
+        assert np.array_equal(_u16(macko_spmv.decompress(got)), oracle.decompress(comp_np)), f"decompress, case {case}"
+        x = (rng.standard_normal(cols) * 0.5).astype(np.float16)
+        y = macko_spmv.multiply(got, torch.from_numpy(x).to(_dev()))
+        _check_y(y, comp_np, x.view(np.uint16), f"multiply, case {case}: {rows}x{cols}")
